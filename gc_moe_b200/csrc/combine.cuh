@@ -1,0 +1,67 @@
+// Weighted-combine tail: y[t] = bf16( sum over the token's valid slots ).
+//
+// The route weights were already applied before the intermediate was
+// requantised, so this is a plain sum: FP32, starting from +0, in the fixed
+// order "shared-expert slot, then top-k slots 0..k-1", skipping slots whose
+// expert id is not a valid expert, then one round to BF16 -- the order of the
+// reference's finalize role (gc_moe/impls/sm100_fp8_fp4_gc_moe.py:549-691).
+// A token without any valid slot gets zeros.  HBM-bound: each thread reduces
+// one 16-byte column group of one token with 16-byte loads and one store.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "device_common.cuh"
+
+namespace gcmoe {
+
+constexpr int kCombineThreads = 256;
+
+struct CombineParams {
+    const __nv_bfloat16* slots;    // combine_tokens [k(+1)][cap][H] on this rank
+    const long long* topk_idx;     // [cap][k]
+    __nv_bfloat16* y;              // [T][H]
+    uint32_t* epoch_word;          // per-call counter in the arena (recv_parity)
+    uint32_t num_tokens, topk, hidden, capacity, num_experts, has_shared;
+};
+
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineParams p) {
+    const uint32_t vecs_per_token = p.hidden / 8;
+    const uint64_t total = static_cast<uint64_t>(p.num_tokens) * vecs_per_token;
+    if (blockIdx.x == 0 && threadIdx.x == 0) *p.epoch_word += 1u;   // one call retired
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kCombineThreads + threadIdx.x; i < total;
+         i += static_cast<uint64_t>(gridDim.x) * kCombineThreads) {
+        const uint32_t t = static_cast<uint32_t>(i / vecs_per_token);
+        const uint32_t v = static_cast<uint32_t>(i - static_cast<uint64_t>(t) * vecs_per_token);
+        float acc[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+        const uint32_t nslots = p.topk + p.has_shared;
+        for (uint32_t g = 0; g < nslots; ++g) {
+            // order: shared slot (index k) first, then 0..k-1
+            const uint32_t slot = p.has_shared ? (g == 0 ? p.topk : g - 1) : g;
+            if (slot < p.topk) {
+                const unsigned long long e = static_cast<unsigned long long>(p.topk_idx[static_cast<size_t>(t) * p.topk + slot]);
+                if (e >= p.num_experts) continue;
+            }
+            const uint4 raw = *reinterpret_cast<const uint4*>(
+                p.slots + (static_cast<size_t>(slot) * p.capacity + t) * p.hidden + v * 8);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                acc[2 * c] = __fadd_rn(acc[2 * c], __uint_as_float(w[c] << 16));
+                acc[2 * c + 1] = __fadd_rn(acc[2 * c + 1], __uint_as_float(w[c] & 0xFFFF0000u));
+            }
+        }
+        uint4 out;
+        uint32_t* o = &out.x;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const __nv_bfloat162 pair = __floats2bfloat162_rn(acc[2 * c], acc[2 * c + 1]);
+            o[c] = *reinterpret_cast<const uint32_t*>(&pair);
+        }
+        *reinterpret_cast<uint4*>(p.y + static_cast<size_t>(t) * p.hidden + v * 8) = out;
+    }
+}
+
+}  // namespace gcmoe

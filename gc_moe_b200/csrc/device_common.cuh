@@ -1,0 +1,108 @@
+// Types shared by the kernels and the host side of the library: the device
+// status block, bounded waits, and the small integer helpers of the pool
+// layout.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "ptx.cuh"
+
+namespace gcmoe {
+
+constexpr int kMaxRanks = 72;
+constexpr int kMaxLocalExperts = 512;
+constexpr int kMaxExperts = 2048;
+
+// Status block in plan-private device memory.  word 0 is zero while every
+// bounded wait of the call has succeeded; the first wait that runs out
+// records where it gave up and the kernels return instead of spinning.
+enum StatusWord : int {
+    kStatusCode = 0,      // 0 = ok, else a StatusCode
+    kStatusKernel = 1,    // KernelId of the reporter
+    kStatusSite = 2,      // wait site inside that kernel
+    kStatusBlock = 3,     // blockIdx.x of the reporter
+    kStatusObserved = 4,  // value seen when the wait gave up
+    kStatusExpected = 5,  // value waited for
+    kStatusAux = 6,
+    kStatusWords = 8
+};
+enum StatusCode : uint32_t { kOk = 0, kWaitTimeout = 1, kBadGeometry = 2 };
+enum KernelId : uint32_t { kKernelDispatch = 1, kKernelGemmL1 = 2, kKernelGemmL2 = 3, kKernelCombine = 4 };
+
+struct WaitCtl {
+    uint32_t* status;          // global status block
+    volatile uint32_t* abort;  // CTA-local abort word in shared memory
+    uint64_t timeout_ns;
+    uint32_t kernel;
+};
+
+__device__ __forceinline__ void report_failure(const WaitCtl& ctl, uint32_t code, uint32_t site,
+                                               uint32_t observed, uint32_t expected) {
+    if (atomicCAS(&ctl.status[kStatusCode], 0u, code) == 0u) {
+        ctl.status[kStatusKernel] = ctl.kernel;
+        ctl.status[kStatusSite] = site;
+        ctl.status[kStatusBlock] = blockIdx.x;
+        ctl.status[kStatusObserved] = observed;
+        ctl.status[kStatusExpected] = expected;
+        __threadfence();
+    }
+    *ctl.abort = 1u;
+}
+
+// Wait for a phase of an mbarrier of this CTA.  Returns false when another
+// role of the CTA has already given up or when the time limit passes; the
+// caller then leaves its loop.  mbarrier.try_wait itself suspends the thread
+// for a bounded, hardware-chosen time, so the loop does not spin hot.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtl& ctl,
+                                          uint32_t site) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 15u) == 0u) {
+            if (*ctl.abort) return false;
+            if (ptx::globaltimer_ns() - t0 > ctl.timeout_ns) {
+                report_failure(ctl, kWaitTimeout, site, parity, 0);
+                return false;
+            }
+        }
+    }
+}
+
+// Wait until a 32-bit flag in (possibly peer-written) global memory reaches
+// `expected`, with acquire semantics at system scope.
+__device__ __forceinline__ bool flag_wait_eq(const uint32_t* flag, uint32_t expected,
+                                             const WaitCtl& ctl, uint32_t site) {
+    uint32_t v = ptx::ld_acquire_sys(flag);
+    if (v == expected) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        v = ptx::ld_acquire_sys(flag);
+        if (v == expected) return true;
+        if ((++spins & 15u) == 0u) {
+            if (*ctl.abort) return false;
+            if (ptx::globaltimer_ns() - t0 > ctl.timeout_ns) {
+                report_failure(ctl, kWaitTimeout, site, v, expected);
+                return false;
+            }
+        }
+        __nanosleep(64);
+    }
+}
+
+__host__ __device__ __forceinline__ uint32_t round_up_u32(uint32_t v, uint32_t m) {
+    return (v + m - 1) / m * m;
+}
+
+// Row, inside a 128-row-aligned scale block, of the block's u-th token: the
+// 4x32 order the tensor core's scale copy expects
+// (gc_moe/gc/__init__.py:19-23).
+__host__ __device__ __forceinline__ uint32_t sf_row_in_block(uint32_t u) {
+    return (u & ~127u) + (u & 31u) * 4u + ((u >> 5) & 3u);
+}
+
+}  // namespace gcmoe

@@ -1,0 +1,371 @@
+// Host side of libgcmoe_sm100.so: argument checks, TMA descriptor encoding,
+// launch configuration and the extern "C" entry points of include/gcmoe.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "../../include/gcmoe.h"
+#include "combine.cuh"
+#include "dispatch.cuh"
+#include "grouped_gemm.cuh"
+
+namespace gcmoe {
+
+thread_local char g_error[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define GCMOE_CUDA(expr)                                                              \
+    do {                                                                              \
+        cudaError_t err__ = (expr);                                                   \
+        if (err__ != cudaSuccess)                                                     \
+            return fail(GCMOE_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
+    } while (0)
+
+// cuTensorMapEncodeTiled is a driver entry point; resolve it through the
+// runtime so the library does not link against libcuda directly.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int get_encoder(EncodeTiledFn* fn) {
+    static EncodeTiledFn cached = nullptr;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        GCMOE_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || sym == nullptr)
+            return fail(GCMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        cached = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    *fn = cached;
+    return GCMOE_OK;
+}
+
+static int encode_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank, uint64_t address,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                      const char* what) {
+    EncodeTiledFn encode;
+    if (int rc = get_encoder(&encode)) return rc;
+    cuuint64_t gdims[5], gstrides[4];
+    cuuint32_t gbox[5], estr[5];
+    for (uint32_t i = 0; i < rank; ++i) { gdims[i] = dims[i]; gbox[i] = box[i]; estr[i] = 1; }
+    for (uint32_t i = 0; i + 1 < rank; ++i) gstrides[i] = strides_bytes[i];
+    CUresult r = encode(map, type, rank, reinterpret_cast<void*>(address), gdims, gstrides, gbox, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(GCMOE_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, int(r));
+    return GCMOE_OK;
+}
+
+static uint32_t pow2_at_least(uint32_t v) {
+    uint32_t r = 32;
+    while (r < v) r <<= 1;
+    return r;
+}
+
+struct Plan {
+    gcmoe_problem prob;
+    gcmoe_buffers buf;
+    int device = 0;
+    int num_sms = 0;
+    uint32_t* status = nullptr;
+    DispatchParams dispatch;
+    GemmParams l1, l2;
+    CombineParams combine;
+    uint32_t dispatch_grid = 1, dispatch_smem = 0;
+    uint32_t gemm_grid_l1 = 1, gemm_grid_l2 = 1, gemm_smem = 0;
+    uint32_t combine_grid = 1;
+};
+
+}  // namespace gcmoe
+
+struct gcmoe_plan : gcmoe::Plan {};
+
+using namespace gcmoe;
+
+static int check_problem(const gcmoe_problem& q) {
+    if (q.num_ranks <= 0 || q.num_ranks > GCMOE_MAX_RANKS || q.rank < 0 || q.rank >= q.num_ranks)
+        return fail(GCMOE_ERR_INVALID, "invalid rank %d of %d", q.rank, q.num_ranks);
+    if (q.num_experts <= 0 || q.num_experts > kMaxExperts || q.num_experts % q.num_ranks ||
+        q.num_experts / q.num_ranks > kMaxLocalExperts)
+        return fail(GCMOE_ERR_INVALID, "invalid rank/expert configuration");
+    if (q.topk <= 0 || q.topk + (q.num_shared_experts > 0) > 32)
+        return fail(GCMOE_ERR_INVALID, "invalid topk/shared configuration");
+    if (q.hidden <= 0 || q.hidden % 256 || q.intermediate <= 0 || q.intermediate % 128 ||
+        q.intermediate > 4096)
+        return fail(GCMOE_ERR_UNSUPPORTED, "hidden must be a multiple of 256 and intermediate a multiple of 128 up to 4096");
+    if (q.capacity <= 0 || q.num_tokens < 0 || q.num_tokens > q.capacity)
+        return fail(GCMOE_ERR_INVALID, "token count %d outside capacity %d", q.num_tokens, q.capacity);
+    const int bm = q.block_m;
+    if (!(bm == 16 || bm == 32 || bm == 64 || bm == 96 || bm == 128 || bm == 192 || bm == 240))
+        return fail(GCMOE_ERR_INVALID, "block_m %d is not a block-M candidate", bm);
+    if (q.ring_tokens <= 0 || q.ring_tokens % 1920 || q.sf_ring_tokens % 4 ||
+        q.sf_ring_tokens < (q.ring_tokens / bm) * int(round_up_u32(bm, 128)))
+        return fail(GCMOE_ERR_INVALID, "invalid ring geometry");
+    // The kernels address the pool without wrap-around: the ring must hold the
+    // largest pool this call can produce.
+    const long long local = q.num_experts / q.num_ranks;
+    const long long routes = 1ll * q.num_ranks * q.capacity * (q.topk < local ? q.topk : local);
+    if (q.ring_tokens < routes + local * (bm - 1))
+        return fail(GCMOE_ERR_UNSUPPORTED, "ring of %d rows cannot hold the whole receive pool", q.ring_tokens);
+    if (q.num_ranks > 1)
+        return fail(GCMOE_ERR_UNSUPPORTED, "multi-rank dispatch is not built into this library version");
+    if (q.num_shared_experts != 0)
+        return fail(GCMOE_ERR_UNSUPPORTED, "the fused shared expert is not built into this library version");
+    return GCMOE_OK;
+}
+
+extern "C" int gcmoe_version(void) { return 100; }
+
+extern "C" const char* gcmoe_last_error(void) { return g_error; }
+
+extern "C" size_t gcmoe_scratch_bytes(const gcmoe_problem* problem) {
+    if (problem == nullptr || problem->num_ranks <= 0) return 0;
+    const size_t local = size_t(problem->num_experts / problem->num_ranks);
+    return round_up_u32(uint32_t(kStatusWords * 4 + (2 * local + 1) * 4), 256);
+}
+
+extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
+                                 gcmoe_plan** out) {
+    if (problem == nullptr || buffers == nullptr || out == nullptr)
+        return fail(GCMOE_ERR_INVALID, "null argument");
+    *out = nullptr;
+    if (int rc = check_problem(*problem)) return rc;
+    const gcmoe_problem& q = *problem;
+    const gcmoe_buffers& b = *buffers;
+    if (b.arena_base[q.rank] == 0 || b.arena_base[q.rank] % 16)
+        return fail(GCMOE_ERR_INVALID, "arena base must be a 16-byte aligned device address");
+    if (b.y % 16) return fail(GCMOE_ERR_INVALID, "y must be 16-byte aligned");
+    if (q.num_tokens > 0 && b.y == 0) return fail(GCMOE_ERR_INVALID, "y is null");
+    if (b.w1 == 0 || b.w2 == 0 || b.w1_sf == 0 || b.w2_sf == 0 || b.w1 % 32 || b.w2 % 32 ||
+        b.w1_sf % 16 || b.w2_sf % 16)
+        return fail(GCMOE_ERR_INVALID, "weights must be 32-byte and scales 16-byte aligned device addresses");
+    if (b.w1_sf_stride < uint64_t(2 * q.intermediate) || b.w1_sf_stride % 4 ||
+        b.w2_sf_stride < uint64_t(q.hidden) || b.w2_sf_stride % 4)
+        return fail(GCMOE_ERR_INVALID, "weight scales must be MN-major with a 4-aligned K stride");
+    if (b.scratch == 0 || b.scratch % 16 || b.scratch_bytes < gcmoe_scratch_bytes(problem))
+        return fail(GCMOE_ERR_INVALID, "scratch block missing or too small");
+
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kPhaseL1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kPhaseL2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kPhaseRaw>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+
+    gcmoe_plan* plan = new (std::nothrow) gcmoe_plan();
+    if (plan == nullptr) return fail(GCMOE_ERR_INVALID, "out of host memory");
+    plan->prob = q;
+    plan->buf = b;
+    auto bail = [&](int rc) { delete plan; return rc; };
+
+    cudaError_t ce = cudaGetDevice(&plan->device);
+    if (ce != cudaSuccess) return bail(fail(GCMOE_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(ce)));
+    int sms = 0, cc_major = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, plan->device);
+    cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, plan->device);
+    if (cc_major != 10)
+        return bail(fail(GCMOE_ERR_UNSUPPORTED, "device compute capability %d.x is not sm_100", cc_major));
+    plan->num_sms = (q.num_sms > 0 && q.num_sms < sms) ? q.num_sms : sms;
+
+    const uint32_t P = q.num_ranks, E = q.num_experts, EL = E / P, H = q.hidden, I = q.intermediate;
+    const uint32_t bm = q.block_m, sfbm = round_up_u32(bm, 128);
+    const uint64_t arena = b.arena_base[q.rank];
+    const uint64_t timeout_ns = uint64_t(q.timeout_ms > 0 ? q.timeout_ms : 2000) * 1000000ull;
+
+    // ---- scratch: status | expert_count[EL] | expert_block_start[EL + 1]
+    plan->status = reinterpret_cast<uint32_t*>(b.scratch);
+    int* expert_count = reinterpret_cast<int*>(b.scratch + kStatusWords * 4);
+    int* expert_block_start = expert_count + EL;
+
+    // ---- dispatch
+    DispatchParams& d = plan->dispatch;
+    memset(&d, 0, sizeof(d));
+    d.x = reinterpret_cast<const uint8_t*>(arena + b.off_x);
+    d.x_sf = reinterpret_cast<const uint32_t*>(arena + b.off_x_sf);
+    d.topk_idx = reinterpret_cast<const long long*>(arena + b.off_topk_idx);
+    d.topk_weights = reinterpret_cast<const float*>(arena + b.off_topk_weights);
+    for (uint32_t r = 0; r < P; ++r) d.arena_base[r] = b.arena_base[r];
+    d.off_recv_count = b.off_recv_count;
+    d.off_recv_count_sum = b.off_recv_count_sum;
+    d.off_routed_pool_blocks = b.off_routed_pool_blocks;
+    d.off_recv_parity = b.off_recv_parity;
+    d.off_index_table = b.off_index_table;
+    d.off_metadata = b.off_metadata;
+    d.off_l1_acts = b.off_l1_acts;
+    d.off_l1_acts_sf = b.off_l1_acts_sf;
+    d.off_l1_weights = b.off_l1_topk_weights;
+    d.expert_count = expert_count;
+    d.expert_block_start = expert_block_start;
+    d.stats = reinterpret_cast<int*>(b.stats);
+    d.status = plan->status;
+    d.timeout_ns = timeout_ns;
+    d.num_ranks = P; d.rank = q.rank; d.num_experts = E; d.local_experts = EL;
+    d.num_tokens = q.num_tokens; d.topk = q.topk; d.hidden = H; d.capacity = q.capacity;
+    d.block_m = bm; d.sf_block_m = sfbm; d.sf_ring = q.sf_ring_tokens;
+    const uint32_t routes = uint32_t(q.num_tokens) * q.topk;
+    const uint32_t warps = kDispatchThreads / 32;
+    uint32_t dgrid = (routes + warps - 1) / warps;
+    dgrid = dgrid < 1 ? 1 : (dgrid > uint32_t(plan->num_sms) ? plan->num_sms : dgrid);
+    plan->dispatch_grid = dgrid;
+    plan->dispatch_smem = dispatch_smem_bytes(E, EL, (routes + dgrid - 1) / dgrid);
+    if (plan->dispatch_smem > uint32_t(kSmemLimit))
+        return bail(fail(GCMOE_ERR_UNSUPPORTED, "dispatch slice does not fit shared memory"));
+
+    // ---- the two grouped GEMMs
+    const uint32_t stages = gemm_pick_stages(bm, sfbm, EL);
+    if (stages < 2) return bail(fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm));
+    plan->gemm_smem = gemm_smem_layout(stages, bm, sfbm, EL).total + 1024;
+    const uint32_t tmem_cols = pow2_at_least(2 * bm + 4 + sfbm / 32);
+    if (tmem_cols > 512) return bail(fail(GCMOE_ERR_UNSUPPORTED, "TMEM budget exceeded"));
+
+    auto fill_common = [&](GemmParams& g, uint32_t w_rows, uint32_t k) {
+        memset(&g, 0, sizeof(g));
+        g.expert_block_start = expert_block_start;
+        g.expert_count = expert_count;
+        g.status = plan->status;
+        g.timeout_ns = timeout_ns;
+        g.w_rows = w_rows;
+        g.k_blocks = k / 128;
+        g.n_tiles = w_rows / 128;
+        g.block_m = bm;
+        g.sf_block_m = sfbm;
+        g.stages = stages;
+        g.local_experts = EL;
+        g.weight_format = 5;
+        g.weight_tx_bytes = 128 * 128 / 2;
+        g.tmem_cols = tmem_cols;
+        g.act_sf_stride = q.sf_ring_tokens;
+        g.capacity = q.capacity;
+        g.hidden = H;
+        g.inter = I;
+    };
+    auto encode_pair = [&](GemmParams& g, uint64_t acts, uint32_t k, uint64_t weights, uint32_t w_rows,
+                           const char* what) -> int {
+        const uint64_t adims[2] = {k, uint64_t(q.ring_tokens)};
+        const uint64_t astr[1] = {k};
+        const uint32_t abox[2] = {128, bm};
+        if (int rc = encode_map(&g.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
+            return rc;
+        // FP4 weights: 128-element (64-byte) rows of one K128 tile are adjacent,
+        // so a 128 x 128 box is one contiguous 8 KiB range in HBM.
+        const uint64_t wdims[4] = {128, w_rows, k / 128, EL};
+        const uint64_t wstr[3] = {64, uint64_t(w_rows) * 64, uint64_t(w_rows) * 64 * (k / 128)};
+        const uint32_t wbox[4] = {128, 128, 1, 1};
+        return encode_map(&g.tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, weights, wdims, wstr, wbox, what);
+    };
+
+    GemmParams& g1 = plan->l1;
+    fill_common(g1, 2 * I, H);
+    if (int rc = encode_pair(g1, arena + b.off_l1_acts, H, b.w1, 2 * I, "gate/up GEMM")) return bail(rc);
+    g1.act_sf = reinterpret_cast<const uint32_t*>(arena + b.off_l1_acts_sf);
+    g1.w_sf = reinterpret_cast<const uint32_t*>(b.w1_sf);
+    g1.w_sf_stride = uint32_t(b.w1_sf_stride);
+    g1.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts);
+    g1.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts_sf);
+    g1.out_sf_stride = q.sf_ring_tokens;
+    g1.route_weight = reinterpret_cast<const float*>(arena + b.off_l1_topk_weights);
+    g1.clamp = q.clamp;
+    g1.has_clamp = q.has_clamp != 0;
+    g1.fast_math = q.fast_math != 0;
+
+    GemmParams& g2 = plan->l2;
+    fill_common(g2, H, I);
+    if (int rc = encode_pair(g2, arena + b.off_l2_acts, I, b.w2, H, "down GEMM")) return bail(rc);
+    g2.act_sf = reinterpret_cast<const uint32_t*>(arena + b.off_l2_acts_sf);
+    g2.w_sf = reinterpret_cast<const uint32_t*>(b.w2_sf);
+    g2.w_sf_stride = uint32_t(b.w2_sf_stride);
+    g2.metadata = reinterpret_cast<const uint32_t*>(arena + b.off_metadata);
+    for (uint32_t r = 0; r < P; ++r) g2.combine_base[r] = b.arena_base[r] + b.off_combine_tokens;
+
+    // Upper bound of pool blocks this call can produce: one partial block per
+    // expert that can be hit, plus the full blocks.
+    const uint64_t all_routes = uint64_t(P) * routes;   // collective calls bring the same order of T
+    uint64_t max_blocks = (all_routes < EL ? all_routes : EL) + all_routes / bm;
+    if (max_blocks < 1) max_blocks = 1;
+    auto grid_for = [&](uint32_t n_tiles) {
+        const uint64_t tiles = max_blocks * n_tiles;
+        return uint32_t(tiles < uint64_t(plan->num_sms) ? tiles : uint64_t(plan->num_sms));
+    };
+    plan->gemm_grid_l1 = grid_for(g1.n_tiles);
+    plan->gemm_grid_l2 = grid_for(g2.n_tiles);
+
+    // ---- combine
+    CombineParams& c = plan->combine;
+    memset(&c, 0, sizeof(c));
+    c.slots = reinterpret_cast<const __nv_bfloat16*>(arena + b.off_combine_tokens);
+    c.topk_idx = reinterpret_cast<const long long*>(arena + b.off_topk_idx);
+    c.y = reinterpret_cast<__nv_bfloat16*>(b.y);
+    c.epoch_word = reinterpret_cast<uint32_t*>(arena + b.off_recv_parity);
+    c.num_tokens = q.num_tokens; c.topk = q.topk; c.hidden = H; c.capacity = q.capacity;
+    c.num_experts = E; c.has_shared = 0;
+    const uint64_t cvecs = uint64_t(q.num_tokens) * (H / 8);
+    uint64_t cgrid = (cvecs + kCombineThreads - 1) / kCombineThreads;
+    const uint64_t cmax = uint64_t(plan->num_sms) * 8;
+    plan->combine_grid = uint32_t(cgrid < 1 ? 1 : (cgrid > cmax ? cmax : cgrid));
+
+    *out = plan;
+    return GCMOE_OK;
+}
+
+extern "C" int gcmoe_plan_destroy(gcmoe_plan* plan) {
+    delete plan;
+    return GCMOE_OK;
+}
+
+extern "C" int gcmoe_kernels_per_launch(const gcmoe_plan* plan) {
+    return plan == nullptr ? 0 : 4;
+}
+
+extern "C" int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned mask, void* cuda_stream) {
+    if (plan == nullptr) return fail(GCMOE_ERR_INVALID, "null plan");
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    if (mask & 1u)
+        dispatch_kernel<<<plan->dispatch_grid, kDispatchThreads, plan->dispatch_smem, s>>>(plan->dispatch);
+    if (mask & 2u)
+        grouped_gemm_kernel<kPhaseL1><<<plan->gemm_grid_l1, kGemmThreads, plan->gemm_smem, s>>>(plan->l1);
+    if (mask & 4u)
+        grouped_gemm_kernel<kPhaseL2><<<plan->gemm_grid_l2, kGemmThreads, plan->gemm_smem, s>>>(plan->l2);
+    if (mask & 8u)
+        combine_kernel<<<plan->combine_grid, kCombineThreads, 0, s>>>(plan->combine);
+    GCMOE_CUDA(cudaGetLastError());
+    return GCMOE_OK;
+}
+
+extern "C" int gcmoe_launch(gcmoe_plan* plan, void* cuda_stream) {
+    return gcmoe_launch_kernels(plan, 15u, cuda_stream);
+}
+
+extern "C" int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* words) {
+    if (plan == nullptr || words == nullptr) return fail(GCMOE_ERR_INVALID, "null argument");
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    GCMOE_CUDA(cudaMemcpyAsync(words, plan->status, kStatusWords * 4, cudaMemcpyDeviceToHost, s));
+    GCMOE_CUDA(cudaStreamSynchronize(s));
+    if (words[kStatusCode] != 0)
+        return fail(GCMOE_ERR_DEVICE,
+                    "device wait gave up: code %u kernel %u site %u block %u observed %u expected %u",
+                    words[kStatusCode], words[kStatusKernel], words[kStatusSite], words[kStatusBlock],
+                    words[kStatusObserved], words[kStatusExpected]);
+    return GCMOE_OK;
+}
+
+extern "C" int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream) {
+    if (plan == nullptr || out == 0) return fail(GCMOE_ERR_INVALID, "null argument");
+    GemmParams g = plan->l1;
+    g.raw_out = reinterpret_cast<float*>(out);
+    grouped_gemm_kernel<kPhaseRaw><<<plan->gemm_grid_l1, kGemmThreads, plan->gemm_smem,
+                                    static_cast<cudaStream_t>(cuda_stream)>>>(g);
+    GCMOE_CUDA(cudaGetLastError());
+    return GCMOE_OK;
+}

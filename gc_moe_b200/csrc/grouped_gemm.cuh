@@ -1,0 +1,436 @@
+// Persistent grouped block-scaled GEMM over the receive pool, one CTA per SM.
+//
+//   out[weight_row, token] = sum_k W[e][weight_row, k] * X[token, k]
+//
+// per pool block (BM tokens of one local expert) and 128-row weight tile.
+// Weights are the MMA's A operand (M = 128), tokens its B operand (N = BM,
+// a multiple of 16), so decode-sized token counts waste no tensor rows and the
+// HBM stream is the weight stream.  Roles (192 threads):
+//   warp 0    one lane issues the TMA / bulk loads of every K128 stage
+//   warp 1    one lane copies the stage's scale words to TMEM and issues the
+//             four K32 tcgen05.mma of the stage; owns the TMEM allocation
+//   warps 2-5 epilogue: read the FP32 accumulator from TMEM (each warp its own
+//             32-lane quarter), fuse the layer's element-wise tail, store
+// Two accumulator stages let the epilogue of tile i overlap the main loop of
+// tile i+1.  The work list is static: tile t = pool_block * n_tiles + n_tile,
+// CTA c takes t = c, c + grid, ... so the CTAs that share a pool block run at
+// the same time and its activation tile is served from L2.
+//
+// Replaces the reference's role-2 compute kernel
+// (gc_moe/impls/sm100_fp8_fp4_gc_moe.py:1108-1905) and its device scheduler
+// (gc_moe/scheduler/gc_moe.py:284-328) for a design whose producers have
+// finished before this kernel starts (stream order), so it needs no task
+// hand-off and no ring flow control.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "device_common.cuh"
+
+namespace gcmoe {
+
+constexpr int kGemmThreads = 192;
+constexpr int kTileRows = 128;             // weight rows per tile = MMA M
+constexpr int kTileK = 128;                // K per pipeline stage = 4 MMAs of K32
+constexpr int kWeightStageBytes = 128 * 128;  // FP4 is unpacked to 8-bit containers by the TMA
+constexpr int kSfChunkBytes = 512;         // 128 rows x one packed int32 of four UE8M0 bytes
+constexpr int kMaxStages = 16;
+constexpr int kSmemLimit = 232448;         // opt-in dynamic shared memory per CTA on sm_100
+
+enum GemmPhase : int { kPhaseL1 = 0, kPhaseL2 = 1, kPhaseRaw = 2 };
+
+struct GemmParams {
+    CUtensorMap tm_act;     // u8 [rows][K], box 128 x BM, 128-byte swizzle
+    CUtensorMap tm_w;       // FP4: 16U4_ALIGN16B [E][K/128][rows][128], box 128 x 128
+                            // FP8: u8 [K/128][rows][128]
+    const uint32_t* act_sf;  // packed scale words, MN-major: word (kb, r) at kb * act_sf_stride + r
+    const uint32_t* w_sf;    // word (e, kb, row) at (e * k_blocks + kb) * w_sf_stride + row
+    const int* expert_block_start;  // [local_experts + 1] pool-block prefix
+    const int* expert_count;        // [local_experts] tokens per local expert
+    uint32_t* status;
+    uint64_t timeout_ns;
+    uint32_t act_sf_stride;  // words between consecutive K128 planes of act_sf
+    uint32_t w_sf_stride;    // words between consecutive K128 planes of w_sf
+    uint32_t w_rows;         // weight rows per expert (2I for the gate/up GEMM, H for the down GEMM)
+    uint32_t k_blocks;       // K / 128
+    uint32_t n_tiles;        // w_rows / 128
+    uint32_t block_m;        // BM
+    uint32_t sf_block_m;     // BM rounded up to 128 (scale rows reserved per pool block)
+    uint32_t stages;
+    uint32_t local_experts;
+    uint32_t weight_format;  // 5 = e2m1 (FP4), 0 = e4m3
+    uint32_t weight_tx_bytes;  // bytes the weight tile's TMA reports to the stage barrier
+    uint32_t tmem_cols;
+    // ---- gate/up epilogue (kPhaseL1)
+    uint8_t* out_acts;        // e4m3 [rows][I]
+    uint8_t* out_sf;          // bytes of the MN-major packed scale ring
+    const float* route_weight;  // [rows]
+    uint32_t out_sf_stride;   // words between K128 planes of out_sf
+    uint32_t inter;           // I
+    float clamp;
+    uint32_t has_clamp;
+    uint32_t fast_math;
+    // ---- down epilogue (kPhaseL2)
+    const uint32_t* metadata;  // (src_rank, src_token, slot) per pool row
+    uint64_t combine_base[kMaxRanks];  // address of combine_tokens on each rank
+    uint32_t capacity;
+    uint32_t hidden;
+    // ---- raw epilogue (kPhaseRaw): FP32 accumulators, [rows][w_rows]
+    float* raw_out;
+};
+
+struct GemmSmemLayout {
+    uint32_t w, a, sfw, sfa, bars, tables, amax, total;
+};
+
+__host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint32_t block_m,
+                                                           uint32_t sf_block_m,
+                                                           uint32_t local_experts) {
+    GemmSmemLayout l;
+    l.w = 0;
+    l.a = l.w + stages * kWeightStageBytes;
+    l.sfw = l.a + stages * block_m * kTileK;
+    l.sfa = l.sfw + stages * kSfChunkBytes;
+    l.bars = l.sfa + stages * sf_block_m * 4;
+    // full[stages], empty[stages], acc_full[2], acc_empty[2], drain, then the
+    // TMEM base slot and the abort word
+    l.tables = l.bars + (2 * stages + 5) * 8 + 16;
+    l.amax = l.tables + round_up_u32((2 * local_experts + 1) * 4, 16);
+    l.total = l.amax + 2 * 4 * 16 * 4;
+    return l;
+}
+
+__host__ inline uint32_t gemm_pick_stages(uint32_t block_m, uint32_t sf_block_m,
+                                          uint32_t local_experts) {
+    for (uint32_t s = kMaxStages; s >= 2; --s) {
+        if (gemm_smem_layout(s, block_m, sf_block_m, local_experts).total + 1024 <= kSmemLimit)
+            return s;
+    }
+    return 0;
+}
+
+// SwiGLU in the reference's op order (impls:122-171): BF16-round the two
+// accumulators, clamp in BF16, FP32 sigmoid, x up, x route weight.
+__device__ __forceinline__ float swiglu_weighted(float gate_acc, float up_acc, float route_w,
+                                                 float clamp_bf16, bool has_clamp,
+                                                 bool fast_math) {
+    float g = __bfloat162float(__float2bfloat16_rn(gate_acc));
+    float u = __bfloat162float(__float2bfloat16_rn(up_acc));
+    if (has_clamp) {
+        g = fminf(g, clamp_bf16);
+        u = fminf(fmaxf(u, -clamp_bf16), clamp_bf16);
+    }
+    float gate;
+    if (fast_math) {
+        const float e = ptx::ex2_approx(__fmul_rn(g, -1.44269502162933349609375f));
+        gate = __fmul_rn(g, ptx::rcp_approx_ftz(__fadd_rn(1.0f, e)));
+    } else {
+        gate = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+    }
+    return __fmul_rn(__fmul_rn(gate, u), route_w);
+}
+
+// Biased exponent of 2^ceil(log2(amax / 448)), floored at 2^-22
+// (gc_moe/common/math.py:146-154).
+__device__ __forceinline__ uint32_t ue8m0_scale_byte(float amax) {
+    uint32_t e = (__float_as_uint(amax) + 0x7FFFFFu - 0x600000u) >> 23;
+    return (e > 113u ? e : 113u) - 8u;
+}
+
+// AND of a predicate over the 128 epilogue threads (named barrier 2).
+__device__ __forceinline__ bool all_epilogue_threads(bool pred) {
+    uint32_t all;
+    asm volatile(
+        "{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, 2, 128, q; "
+        "selp.u32 %0, 1, 0, p; }"
+        : "=r"(all)
+        : "r"(static_cast<uint32_t>(pred))
+        : "memory");
+    return all != 0;
+}
+
+template <int kPhase>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
+    uint8_t* const gbase = smem_raw + (base - raw_addr);
+
+    const GemmSmemLayout L = gemm_smem_layout(p.stages, p.block_m, p.sf_block_m, p.local_experts);
+    const uint32_t bar_full = base + L.bars;
+    const uint32_t bar_empty = bar_full + p.stages * 8;
+    const uint32_t bar_acc_full = bar_empty + p.stages * 8;
+    const uint32_t bar_acc_empty = bar_acc_full + 16;
+    const uint32_t bar_drain = bar_acc_empty + 16;
+    volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L.bars + (2 * p.stages + 5) * 8);
+    volatile uint32_t* const abort_word = tmem_slot + 1;
+    int* const tbl_start = reinterpret_cast<int*>(gbase + L.tables);      // [E_loc + 1]
+    int* const tbl_count = tbl_start + p.local_experts + 1;               // [E_loc]
+    float* const amax_x = reinterpret_cast<float*>(gbase + L.amax);       // [2][4][16]
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+
+    WaitCtl ctl;
+    ctl.status = p.status;
+    ctl.abort = abort_word;
+    ctl.timeout_ns = p.timeout_ns;
+    ctl.kernel = kPhase == kPhaseL2 ? kKernelGemmL2 : kKernelGemmL1;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            ptx::mbar_init(bar_full + 8 * s, 1);
+            ptx::mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (uint32_t i = 0; i < 2; ++i) {
+            ptx::mbar_init(bar_acc_full + 8 * i, 1);
+            ptx::mbar_init(bar_acc_empty + 8 * i, 4);   // one arrival per epilogue warp
+        }
+        ptx::mbar_init(bar_drain, 1);
+        *abort_word = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&p.tm_act);
+        ptx::prefetch_tensormap(&p.tm_w);
+    }
+    for (uint32_t i = threadIdx.x; i <= p.local_experts; i += kGemmThreads)
+        tbl_start[i] = p.expert_block_start[i];
+    for (uint32_t i = threadIdx.x; i < p.local_experts; i += kGemmThreads)
+        tbl_count[i] = p.expert_count[i];
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), p.tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const uint32_t pool_blocks = static_cast<uint32_t>(tbl_start[p.local_experts]);
+    const uint32_t total_tiles = pool_blocks * p.n_tiles;
+    const uint32_t bm = p.block_m;
+
+    // Local expert that owns pool block b: last l with start[l] <= b.
+    auto expert_of_block = [&](uint32_t b) -> uint32_t {
+        uint32_t lo = 0, hi = p.local_experts;   // start[lo] <= b < start[hi]
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (static_cast<uint32_t>(tbl_start[mid]) <= b) lo = mid; else hi = mid;
+        }
+        return lo;
+    };
+    auto valid_rows = [&](uint32_t b, uint32_t e) -> uint32_t {
+        const uint32_t left = static_cast<uint32_t>(tbl_count[e]) - (b - static_cast<uint32_t>(tbl_start[e])) * bm;
+        return left < bm ? left : bm;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ loads
+        if (lane == 0) {
+            const uint32_t tx = p.weight_tx_bytes + kSfChunkBytes + bm * kTileK + p.sf_block_m * 4;
+            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const uint32_t b = tile / p.n_tiles, nt = tile - b * p.n_tiles;
+                const uint32_t e = expert_of_block(b);
+                const uint32_t* wsf = p.w_sf + static_cast<size_t>(e) * p.k_blocks * p.w_sf_stride + nt * kTileRows;
+                const uint32_t* asf = p.act_sf + static_cast<size_t>(b) * p.sf_block_m;
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, ctl, 1)) { ok = false; break; }
+                    const uint32_t full = bar_full + 8 * stage;
+                    ptx::mbar_arrive_expect_tx(full, tx);
+                    armed |= 1u << stage;
+                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    if (p.weight_format == 5u)
+                        ptx::tma_load_4d(base + L.w + stage * kWeightStageBytes, &p.tm_w, full, 0,
+                                         nt * kTileRows, kb, e, ptx::kEvictFirst);
+                    else
+                        ptx::tma_load_3d(base + L.w + stage * kWeightStageBytes, &p.tm_w, full, 0,
+                                         nt * kTileRows, kb, ptx::kEvictFirst);
+                    ptx::bulk_load_1d(base + L.sfw + stage * kSfChunkBytes,
+                                      wsf + static_cast<size_t>(kb) * p.w_sf_stride, kSfChunkBytes,
+                                      full, ptx::kEvictFirst);
+                    ptx::tma_load_2d(base + L.a + stage * bm * kTileK, &p.tm_act, full, kb * kTileK,
+                                     b * bm, ptx::kEvictLast);
+                    ptx::bulk_load_1d(base + L.sfa + stage * p.sf_block_m * 4,
+                                      asf + static_cast<size_t>(kb) * p.act_sf_stride,
+                                      p.sf_block_m * 4, full, ptx::kEvictLast);
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Another role gave up.  Let the copies already in flight land
+                // (they depend on nothing) before the CTA releases its memory.
+                const uint64_t t0 = ptx::globaltimer_ns();
+                for (uint32_t s = 0; s < p.stages; ++s) {
+                    if (!(armed >> s & 1u)) continue;
+                    while (!ptx::mbar_try_wait(bar_full + 8 * s, (armed_parity >> s) & 1u) &&
+                           ptx::globaltimer_ns() - t0 < 2000000ull) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t sfw_tmem = tmem_base + 2 * bm;        // 4 columns
+            const uint32_t sfa_tmem = sfw_tmem + 4;              // sf_block_m / 32 columns
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const uint32_t b = tile / p.n_tiles;
+                const uint32_t e = expert_of_block(b);
+                const uint32_t n = round_up_u32(valid_rows(b, e), 16);
+                const uint32_t idesc = ptx::instr_desc(n, p.weight_format);
+                const uint32_t as = it & 1u;
+                if (!mbar_wait(bar_acc_empty + 8 * as, ((it >> 1) & 1u) ^ 1u, ctl, 2)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * bm;
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, ctl, 3)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t sfw_s = base + L.sfw + stage * kSfChunkBytes;
+                    const uint32_t sfa_s = base + L.sfa + stage * p.sf_block_m * 4;
+                    ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
+                    ptx::tmem_cp_sf(sfa_tmem, ptx::smem_desc(sfa_s, 128, false));
+                    if (p.sf_block_m > 128)
+                        ptx::tmem_cp_sf(sfa_tmem + 4, ptx::smem_desc(sfa_s + kSfChunkBytes, 128, false));
+                    const uint64_t wdesc = ptx::smem_desc(base + L.w + stage * kWeightStageBytes, 1024, true);
+                    const uint64_t adesc = ptx::smem_desc(base + L.a + stage * bm * kTileK, 1024, true);
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {
+                        // 32 K elements = 32 bytes in the swizzled row = +2 in 16-byte units;
+                        // scale byte k of the stage's packed word for both operands.
+                        ptx::mma_mxf8f6f4(d_tmem, wdesc + 2 * k, adesc + 2 * k,
+                                          idesc | (k << 29) | (k << 4), sfw_tmem, sfa_tmem,
+                                          (kb | k) != 0u);
+                    }
+                    ptx::tc_commit(bar_empty + 8 * stage);
+                    if (kb + 1 == p.k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
+                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Do not free TMEM under MMAs that may still be running.
+                ptx::tc_commit(bar_drain);
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while (!ptx::mbar_try_wait(bar_drain, 0) && ptx::globaltimer_ns() - t0 < 2000000ull) {}
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const uint32_t q = warp & 3u;           // the TMEM lane quarter this warp can read
+        const uint32_t r = q * 32 + lane;       // weight row inside the tile
+        const uint32_t lane_base = (q * 32) << 16;
+        uint32_t it = 0;
+        uint32_t xbuf = 0;
+        bool ok = true;
+        const float clamp_bf16 = __bfloat162float(__float2bfloat16_rn(p.clamp));
+        for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+            const uint32_t b = tile / p.n_tiles, nt = tile - b * p.n_tiles;
+            const uint32_t e = expert_of_block(b);
+            const uint32_t valid = valid_rows(b, e);
+            const uint32_t ncols = round_up_u32(valid, 16);
+            const uint32_t as = it & 1u;
+            const uint32_t row0 = b * bm;       // pool row of accumulator column 0
+            // Every epilogue thread must take the same exit, or the named barrier
+            // below would wait for threads that have left: vote on the outcome.
+            if (!all_epilogue_threads(mbar_wait(bar_acc_full + 8 * as, (it >> 1) & 1u, ctl, 4))) {
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after();
+            for (uint32_t c0 = 0; c0 < ncols; c0 += 16) {
+                uint32_t vi[16];
+                ptx::tmem_ld16(tmem_base + lane_base + as * bm + c0, vi);
+                ptx::tmem_ld_wait();
+                if (c0 + 16 >= ncols) {
+                    // Last read of this accumulator stage: hand it back to the MMA warp.
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar_acc_empty + 8 * as);
+                }
+                if constexpr (kPhase == kPhaseRaw) {
+#pragma unroll
+                    for (uint32_t c = 0; c < 16; ++c) {
+                        const uint32_t col = c0 + c;
+                        if (col < valid)
+                            p.raw_out[static_cast<size_t>(row0 + col) * p.w_rows + nt * kTileRows + r] =
+                                __uint_as_float(vi[c]);
+                    }
+                } else if constexpr (kPhase == kPhaseL2) {
+#pragma unroll
+                    for (uint32_t c = 0; c < 16; ++c) {
+                        const uint32_t col = c0 + c;
+                        if (col < valid) {
+                            const uint32_t* m = p.metadata + static_cast<size_t>(row0 + col) * 3;
+                            const uint32_t src_rank = m[0], src_token = m[1], slot = m[2];
+                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.combine_base[src_rank]) +
+                                (static_cast<size_t>(slot) * p.capacity + src_token) * p.hidden +
+                                nt * kTileRows + r;
+                            *dst = __float2bfloat16_rn(__uint_as_float(vi[c]));
+                        }
+                    }
+                } else {
+                    // Rows come in groups of 16: 8 gate rows then the 8 up rows of the
+                    // same channels, so lane l and lane l^8 hold a channel's pair.  The
+                    // gate lane finishes the even columns, the up lane the odd ones.
+                    const uint32_t is_up = (r >> 3) & 1u;
+                    const uint32_t ch = nt * 64 + (r >> 4) * 8 + (r & 7u);   // intermediate channel
+                    float res[8], amax[8];
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        const float even = __uint_as_float(vi[2 * j]), odd = __uint_as_float(vi[2 * j + 1]);
+                        const float recv = __shfl_xor_sync(0xffffffffu, is_up ? even : odd, 8);
+                        const float g = is_up ? recv : even;
+                        const float u = is_up ? odd : recv;
+                        const uint32_t col = c0 + 2 * j + is_up;
+                        const float w = col < valid ? p.route_weight[row0 + col] : 0.0f;
+                        res[j] = swiglu_weighted(g, u, w, clamp_bf16, p.has_clamp != 0, p.fast_math != 0);
+                        float a = fabsf(res[j]);
+                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+                        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+                        amax[j] = a;     // max over this warp's 16 channels of column `col`
+                    }
+                    // A scale covers 32 channels = this warp and its neighbour (q ^ 1).
+                    float* const mine = amax_x + (xbuf * 4 + q) * 16;
+                    const float* const other = amax_x + (xbuf * 4 + (q ^ 1u)) * 16;
+                    if ((lane & 0x17u) == 0u) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 8; ++j) mine[2 * j + is_up] = amax[j];
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        const uint32_t col = c0 + 2 * j + is_up;
+                        const float m = fmaxf(amax[j], other[2 * j + is_up]);
+                        const uint32_t code = ue8m0_scale_byte(m);
+                        const float inv = __uint_as_float((254u - code) << 23);
+                        const uint32_t byte = ptx::cvt_e4m3x2(__fmul_rn(res[j], inv), 0.0f) & 0xFFu;
+                        if (col < valid) {
+                            p.out_acts[static_cast<size_t>(row0 + col) * p.inter + ch] = static_cast<uint8_t>(byte);
+                            if ((q & 1u) == 0u && (lane & 0x17u) == 0u) {
+                                const uint32_t k32 = nt * 2 + (q >> 1);   // index of the 32-channel group
+                                const size_t word = static_cast<size_t>(k32 >> 2) * p.out_sf_stride +
+                                                    static_cast<size_t>(b) * p.sf_block_m + sf_row_in_block(col);
+                                p.out_sf[word * 4 + (k32 & 3u)] = static_cast<uint8_t>(code);
+                            }
+                        }
+                    }
+                    xbuf ^= 1u;
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, p.tmem_cols);
+    }
+}
+
+}  // namespace gcmoe

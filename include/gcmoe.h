@@ -1,0 +1,139 @@
+/*
+ * C ABI of libgcmoe_sm100.so: the B200 (sm_100a) implementation of the
+ * fp8 x fp4 MoE layer behind the reference operator's Python API.
+ *
+ * The library replaces everything below the reference's launch seam
+ *   launch_gc_moe(config, y, l1_weights, l2_weights, call_buffer, shared_l1,
+ *                 shared_l2, stats)
+ *   (gc_moe/jit_kernels/impls/sm100_fp8_fp4_gc_moe.py:721-727)
+ * i.e. its JIT (gc_moe/runtime/jit.py), its launch runtime
+ * (gc_moe/runtime/gc_moe.py:369-418) and its role kernels
+ * (gc_moe/impls/sm100_fp8_fp4_gc_moe.py).  Plain C types only: pointers are
+ * device addresses passed as integers, sizes are element counts, and every
+ * function returns 0 on success or a negative gcmoe_error; the message of the
+ * last failure on the calling thread is available from gcmoe_last_error().
+ *
+ * Nothing here allocates device memory unless its comment says so: the caller
+ * owns the symmetric arena, the weights, the output and the scratch block.
+ */
+#ifndef GCMOE_H_
+#define GCMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GCMOE_MAX_RANKS 72
+#define GCMOE_STATUS_WORDS 8
+
+typedef enum gcmoe_error {
+    GCMOE_OK = 0,
+    GCMOE_ERR_INVALID = -1,     /* contract violation in the arguments          */
+    GCMOE_ERR_UNSUPPORTED = -2, /* geometry the kernels do not cover            */
+    GCMOE_ERR_CUDA = -3,        /* a CUDA runtime or driver call failed         */
+    GCMOE_ERR_DEVICE = -4       /* a kernel's bounded wait ran out (see status) */
+} gcmoe_error;
+
+/* Geometry of one call.  Mirrors the reference's ValidatedCall
+ * (gc_moe/apis/gc_moe.py:19-31) plus the buffer geometry it reads from
+ * GCSymmBuffer (gc_moe/gc/__init__.py:35-58). */
+typedef struct gcmoe_problem {
+    int32_t num_ranks;          /* P, ranks of the expert-parallel group        */
+    int32_t rank;               /* this rank                                    */
+    int32_t num_experts;        /* E, routed experts over all ranks             */
+    int32_t capacity;           /* token capacity per rank (1920-aligned)       */
+    int32_t topk;               /* k                                            */
+    int32_t hidden;             /* H                                            */
+    int32_t intermediate;       /* I of one routed expert                       */
+    int32_t num_tokens;         /* T of this call on this rank (= y.shape[0])   */
+    int32_t block_m;            /* get_block_m_for_gc_moe(...) for this call    */
+    int32_t ring_tokens;        /* rows of l1_acts / l2_acts                    */
+    int32_t sf_ring_tokens;     /* rows of the two scale rings                  */
+    int32_t num_shared_experts; /* 0 or the fused shared expert's I / I_routed  */
+    int32_t shared_gran_k;      /* 32 or 128: K granularity of shared weight SF */
+    int32_t has_clamp;          /* activation_clamp given                       */
+    float clamp;                /* its value                                    */
+    int32_t fast_math;          /* approx exp2/rcp in the SwiGLU sigmoid        */
+    int32_t timeout_ms;         /* limit of every device-side wait (0 = 2000)   */
+    int32_t num_sms;            /* SMs to use (0 = all of the device)           */
+} gcmoe_problem;
+
+/* Device addresses.  `arena_base[r]` is rank r's symmetric arena as mapped in
+ * THIS process (GCSymmBuffer.peer_addresses, gc_moe/gc/__init__.py:64-69);
+ * the off_* members are byte offsets inside an arena, taken from the
+ * reference-compatible layout (gc_moe/layout/gc_moe.py:110-251). */
+typedef struct gcmoe_buffers {
+    uint64_t arena_base[GCMOE_MAX_RANKS];
+    uint64_t off_recv_parity, off_routed_pool_blocks;
+    uint64_t off_recv_count, off_recv_count_sum;
+    uint64_t off_index_table, off_metadata;
+    uint64_t off_x, off_x_sf, off_topk_idx, off_topk_weights;
+    uint64_t off_l1_acts, off_l1_acts_sf, off_l1_topk_weights;
+    uint64_t off_l2_acts, off_l2_acts_sf, off_combine_tokens;
+    uint64_t off_shared_l1_acts_sf, off_shared_l2_acts, off_shared_l2_acts_sf;
+    uint64_t shared_sf_rows;      /* rows of the two shared scale views          */
+    uint64_t y;                   /* bf16 [T, H], 16-byte aligned                */
+    uint64_t stats;               /* int32 [E/P] cumulative counter, or 0        */
+    uint64_t w1, w1_sf;           /* int8 [E/P, H/128, 2I, 64]; int32 MN-major   */
+    uint64_t w2, w2_sf;           /* int8 [E/P, I/128, H, 64];  int32 MN-major   */
+    uint64_t w1_sf_stride, w2_sf_stride;   /* words between K128 planes          */
+    uint64_t sw1, sw1_sf, sw2, sw2_sf;     /* fused shared expert, or 0          */
+    uint64_t sw1_sf_stride, sw2_sf_stride;
+    uint64_t scratch;             /* gcmoe_scratch_bytes() bytes, zero-filled    */
+    uint64_t scratch_bytes;
+} gcmoe_buffers;
+
+typedef struct gcmoe_plan gcmoe_plan;
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int gcmoe_version(void);
+
+/* Message of the last error returned on this thread ("" if none). */
+const char* gcmoe_last_error(void);
+
+/* Bytes of plan-private device scratch a plan for `problem` needs (status
+ * block, per-expert counts, pool-block prefix).  The caller allocates and
+ * zero-fills it once. */
+size_t gcmoe_scratch_bytes(const gcmoe_problem* problem);
+
+/* Validate the geometry, encode the TMA descriptors and precompute the launch
+ * configuration of the layer's kernels.  Replaces prepare_role_binaries
+ * (gc_moe/jit_kernels/impls/sm100_fp8_fp4_gc_moe.py:551-719).  No device
+ * memory is allocated; the plan stays valid while the addresses in `buffers`
+ * do. */
+int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
+                      gcmoe_plan** plan);
+int gcmoe_plan_destroy(gcmoe_plan* plan);
+
+/* Enqueue one layer call (dispatch, gate/up GEMM, down GEMM, combine) on
+ * `cuda_stream` (a cudaStream_t).  Plain stream launches: a caller that is
+ * capturing the stream into a CUDA graph captures the layer.  Replaces
+ * GreenContextPair.launch (gc_moe/runtime/gc_moe.py:369-418). */
+int gcmoe_launch(gcmoe_plan* plan, void* cuda_stream);
+
+/* Enqueue only the kernels selected by `kernel_mask` (bit 0 dispatch, bit 1
+ * gate/up GEMM, bit 2 down GEMM, bit 3 combine); used by the parity tests and
+ * for per-kernel timing. */
+int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned kernel_mask, void* cuda_stream);
+
+/* Number of kernels gcmoe_launch enqueues per call. */
+int gcmoe_kernels_per_launch(const gcmoe_plan* plan);
+
+/* Copy the plan's device status block to `words` (GCMOE_STATUS_WORDS values)
+ * after synchronising `cuda_stream`.  Returns GCMOE_ERR_DEVICE if a bounded
+ * wait ran out; the reference traps the GPU instead
+ * (gc_moe/comm/gc_barrier.py:44-80). */
+int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* words);
+
+/* Raw grouped GEMM over an already dispatched pool: FP32 accumulators of
+ * W1 x pool rows to `out` ([pool rows][2I] floats).  Test hook for the MMA,
+ * descriptor and scale plumbing. */
+int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GCMOE_H_ */
