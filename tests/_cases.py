@@ -1,0 +1,109 @@
+"""Shared helpers of the GPU parity tests: build one seeded layer problem,
+run it through the public operator API, and fetch the arena data products."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import gc_moe_b200 as G
+from gc_moe_b200.layout import round_up, sf_row_in_block
+from oracle import gcmoe_oracle as O
+
+DEV = 'cuda'
+
+
+class LayerCase:
+    """One world-1 problem: quantised weights on the GPU in operator layout,
+    a workspace, and the original CPU tensors for the oracle."""
+
+    def __init__(self, group, num_experts, hidden, inter, topk, capacity=1920, seed=0, weight_std=0.02):
+        self.e, self.h, self.i, self.k = num_experts, hidden, inter, topk
+        self.capacity = capacity
+        # Quantise on the GPU (seconds instead of a minute at benchmark sizes);
+        # the oracle gets CPU copies of the very same bytes.
+        from gc_moe_b200 import quant
+        g = torch.Generator(device=DEV).manual_seed(seed)
+        gpu = []
+        for rows, k in ((2 * inter, hidden), (hidden, inter)):
+            payload = torch.empty((num_experts, rows, k // 2), dtype=torch.int8, device=DEV)
+            codes = torch.empty((num_experts, rows, k // 32), dtype=torch.uint8, device=DEV)
+            for e in range(num_experts):
+                w = torch.randn((rows, k), device=DEV, generator=g) * weight_std
+                payload[e], codes[e] = quant.quantize_weights_fp4(w)
+            gpu.append((payload, codes))
+        (self.q1, self.c1), (self.q2, self.c2) = [(a.cpu(), b.cpu()) for a, b in gpu]
+        self.buf = G.get_symm_buffer_for_gc_moe(group, num_experts, capacity, topk, hidden, inter)
+        self.l1, self.l2 = G.transform_weights_for_gc_moe(
+            (gpu[0][0], quant.weight_scales_mn_major(gpu[0][1])),
+            (gpu[1][0], quant.weight_scales_mn_major(gpu[1][1])))
+
+    def block_m(self, tokens):
+        return G.get_block_m_for_gc_moe(1, self.e, self.buf.num_max_tokens_per_rank, tokens, self.k)
+
+    def stage(self, xq, xsf, idx, w):
+        t = xq.shape[0]
+        self.buf.x[:t].copy_(xq.to(DEV))
+        self.buf.x_sf[:t].copy_(xsf.to(DEV))
+        self.buf.topk_idx[:t].copy_(idx.to(DEV))
+        self.buf.topk_weights[:t].copy_(w.to(DEV))
+
+    def run(self, xq, xsf, idx, w, clamp=10.0, fast_math=True, stats=None, y=None, guard=0):
+        """Stage the inputs, call the operator, return y on the CPU.  With
+        `guard` rows of NaN around y the caller can check nothing else is written."""
+        t = xq.shape[0]
+        self.stage(xq, xsf, idx, w)
+        if y is None:
+            full = torch.full((t + 2 * guard, self.h), float('nan'), dtype=torch.bfloat16, device=DEV)
+            y = full[guard:guard + t]
+            self.full_y = full
+        G.fp8_fp4_gc_moe(y, self.l1, self.l2, self.buf, cumulative_local_expert_recv_stats=stats,
+                         activation_clamp=clamp, fast_math=fast_math)
+        torch.cuda.synchronize()
+        self.buf.raise_on_device_error()
+        return y.cpu()
+
+    def oracle(self, xq, xsf, idx, w, clamp=10.0):
+        return O.moe_layer([xq], [xsf], [idx], [w], self.q1, self.c1, self.q2, self.c2,
+                           [self.block_m(xq.shape[0])], clamp=clamp)
+
+    # ---- arena data products of the last call (generation = parity before the call)
+    def products(self, tokens, generation):
+        lay, bm = self.buf.layout, self.block_m(tokens)
+        e = self.e
+        out = {}
+        out['counts'] = self.buf.region('expert_recv_count').view(torch.int64)[generation * e:(generation + 1) * e].cpu().numpy()
+        out['count_sum'] = (self.buf.region('expert_recv_count_sum').view(torch.int64)[generation * e:(generation + 1) * e]
+                            .cpu().numpy() & 0xFFFFFFFF)
+        out['pool_blocks'] = int(self.buf.region('routed_pool_blocks').view(torch.int32)[0])
+        rows = out['pool_blocks'] * bm
+        out['metadata'] = self.buf.region('token_src_metadata').view(torch.int32).reshape(-1, 3)[:rows].cpu().numpy()
+        out['index_table'] = self.buf.region('src_token_topk_idx').view(torch.int32).reshape(e, 1, lay.capacity).cpu().numpy()
+        out['l1_acts'] = self.buf.l1_acts.view(torch.uint8)[:rows].cpu().numpy()
+        out['l1_weights'] = self.buf.buffer.narrow(0, lay.views['l1_topk_weights'].offset, rows * 4).view(torch.float32).cpu().numpy()
+        sf_rows = out['pool_blocks'] * round_up(bm, 128)
+        out['l1_acts_sf'] = self.buf.l1_acts_sf[:sf_rows].cpu().numpy()
+        out['l2_acts'] = self.buf.l2_acts.view(torch.uint8)[:rows].cpu().numpy()
+        out['l2_acts_sf'] = np.ascontiguousarray(self.buf.l2_acts_sf[:sf_rows].cpu().numpy()).view(np.uint8)
+        return out
+
+    def close(self):
+        self.buf.destroy()
+
+
+def sf_rows_of_pool(rows, bm):
+    """Scale-ring row of each pool row."""
+    return np.array([(r // bm) * round_up(bm, 128) + sf_row_in_block(r % bm) for r in rows], dtype=np.int64)
+
+
+def check_dispatch_products(prod, d, bm):
+    """Exact comparison of the arena's dispatch data products with the oracle's."""
+    assert np.array_equal(prod['counts'], d.counts[0])
+    assert np.array_equal(prod['count_sum'], d.counts.sum(0))
+    assert prod['pool_blocks'] == d.pool_blocks
+    valid = np.nonzero(d.metadata[:, 0] >= 0)[0]
+    assert np.array_equal(prod['metadata'][valid], d.metadata[valid])
+    assert np.array_equal(prod['l1_acts'][valid], d.rows[valid])
+    assert np.array_equal(prod['l1_weights'][valid], d.weights[valid])
+    assert np.array_equal(prod['l1_acts_sf'][sf_rows_of_pool(valid, bm)], d.sf_words[valid])
+    for (l, s), lst in d.index_lists.items():
+        assert np.array_equal(prod['index_table'][l, s, :len(lst)].astype(np.uint32), lst)

@@ -1,0 +1,69 @@
+"""The C-ABI library loads on a machine without a GPU and exports every
+function include/gcmoe.h declares, with the struct sizes the binding assumes."""
+import ctypes
+import os
+import re
+import subprocess
+
+import pytest
+
+from gc_moe_b200 import _native, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, 'include', 'gcmoe.h')
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+    return sorted(set(re.findall(r'\b(gcmoe_[a-z0-9_]+)\s*\(', text)))
+
+
+@pytest.fixture(scope='module')
+def lib():
+    build.build()
+    return _native.library()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_functions()
+    assert len(names) >= 10
+    for name in names:
+        assert hasattr(lib, name), name
+    assert sorted(_native.EXPORTED_SYMBOLS) == names
+
+
+def test_struct_sizes_match_the_header(tmp_path):
+    src = tmp_path / 'sizes.c'
+    src.write_text('#include <stdio.h>\n#include "gcmoe.h"\nint main(void){printf("%zu %zu %zu %zu\\n",'
+                   'sizeof(gcmoe_problem),sizeof(gcmoe_buffers),offsetof(gcmoe_buffers,y),'
+                   'offsetof(gcmoe_problem,clamp));return 0;}\n')
+    exe = tmp_path / 'sizes'
+    subprocess.run(['gcc', '-I', os.path.join(ROOT, 'include'), str(src), '-o', str(exe)], check=True)
+    sizes = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    assert sizes == [ctypes.sizeof(_native.Problem), ctypes.sizeof(_native.Buffers),
+                     _native.Buffers.y.offset, _native.Problem.clamp.offset]
+
+
+def test_version_and_argument_errors_need_no_gpu(lib):
+    assert lib.gcmoe_version() >= 100
+    prob = _native.Problem(num_ranks=1, rank=0, num_experts=8, capacity=1920, topk=2, hidden=1024,
+                           intermediate=512, num_tokens=4, block_m=16, ring_tokens=5760,
+                           sf_ring_tokens=46080)
+    assert lib.gcmoe_scratch_bytes(ctypes.byref(prob)) >= 8 * 4 + 17 * 4
+    handle = ctypes.c_void_p()
+    bufs = _native.Buffers()
+    for bad, exc in ((dict(block_m=24), ValueError), (dict(hidden=1000), NotImplementedError),
+                     (dict(num_tokens=5000), ValueError), (dict(rank=3), ValueError),
+                     (dict(ring_tokens=1920), NotImplementedError)):
+        p = _native.Problem.from_buffer_copy(prob)
+        for k, v in bad.items():
+            setattr(p, k, v)
+        rc = lib.gcmoe_plan_create(ctypes.byref(p), ctypes.byref(bufs), ctypes.byref(handle))
+        assert rc < 0 and not handle.value
+        with pytest.raises(exc):
+            _native.raise_for(rc)
+    # a well-formed problem with null buffers is a contract violation, not a crash
+    rc = lib.gcmoe_plan_create(ctypes.byref(prob), ctypes.byref(bufs), ctypes.byref(handle))
+    assert rc == _native.ERR_INVALID and 'arena' in _native.last_error()
+    assert lib.gcmoe_launch(None, None) == _native.ERR_INVALID

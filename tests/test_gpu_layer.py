@@ -1,0 +1,192 @@
+"""GPU parity: the CUDA layer, called through the operator API (and so through
+the C ABI), against the CPU oracle on the same seeded inputs.
+
+Integer products (counts, pool layout, index table, metadata, dispatched rows
+and scales) must be bit-exact.  BF16 outputs: cosine >= 0.9999 and a maximum
+error, relative to the largest output magnitude, of at most 2^-6 (two BF16
+ulps of the largest value) -- in practice the outputs are bit-identical except
+where a differently ordered FP32 accumulation flips one BF16/FP8 rounding.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import gcmoe_oracle as O
+
+from _cases import LayerCase, check_dispatch_products, sf_rows_of_pool
+
+pytestmark = pytest.mark.gpu
+
+COSINE_MIN = 0.9999
+MAX_REL_ERR = 2.0 ** -6
+
+
+def assert_close(y, ref):
+    assert torch.isfinite(y.float()).all()
+    assert O.cosine(y, ref) >= COSINE_MIN
+    assert O.max_rel_err(y, ref) <= MAX_REL_ERR
+
+
+@pytest.fixture(scope='module')
+def small(single_rank_group):
+    case = LayerCase(single_rank_group, num_experts=8, hidden=1024, inter=512, topk=2, seed=0)
+    yield case
+    case.close()
+
+
+@pytest.fixture(scope='module')
+def config1(single_rank_group):
+    """Single-GPU benchmark geometry: hidden 4096, 64 experts, top-8, intermediate 2048."""
+    case = LayerCase(single_rank_group, num_experts=64, hidden=4096, inter=2048, topk=8, seed=1)
+    yield case
+    case.close()
+
+
+def parity(case):
+    return int(case.buf.region('recv_parity').view(torch.int32)[0].item())
+
+
+def test_config0_bit_exact_products_and_output(small):
+    xq, xsf, idx, w = O.make_tokens(16, small.h, small.e, small.k, seed=1)
+    gen = parity(small) & 1
+    stats = torch.zeros(small.e, dtype=torch.int32, device='cuda')
+    y = small.run(xq, xsf, idx, w, fast_math=False, stats=stats, guard=2)
+    ref = small.oracle(xq, xsf, idx, w)
+    bm = small.block_m(16)
+    prod = small.products(16, gen)
+    check_dispatch_products(prod, ref.dispatch[0], bm)
+    assert np.array_equal(stats.cpu().numpy(), ref.stats[0])
+    valid = np.nonzero(ref.dispatch[0].metadata[:, 0] >= 0)[0]
+    assert (prod['l2_acts'][valid] == ref.l2_acts[0].view(torch.uint8).numpy()[valid]).mean() > 0.999
+    got_sf = prod['l2_acts_sf'][sf_rows_of_pool(valid, bm)].reshape(len(valid), -1)
+    assert (got_sf == ref.l2_sf[0].numpy()[valid]).mean() > 0.999
+    assert_close(y, ref.y[0])
+    # nothing outside y[:T] is written
+    guard = small.full_y.cpu()
+    assert torch.isnan(guard[:2].float()).all() and torch.isnan(guard[-2:].float()).all()
+
+
+@pytest.mark.parametrize('tokens', [1, 8, 32, 128, 256])
+def test_config1_token_sweep(config1, tokens):
+    xq, xsf, idx, w = O.make_tokens(tokens, config1.h, config1.e, config1.k, seed=100 + tokens)
+    gen = parity(config1) & 1
+    y = config1.run(xq, xsf, idx, w)
+    ref = config1.oracle(xq, xsf, idx, w)
+    check_dispatch_products(config1.products(tokens, gen), ref.dispatch[0], config1.block_m(tokens))
+    assert_close(y, ref.y[0])
+
+
+@pytest.mark.parametrize('tokens', [0, 3, 79, 81, 193, 450])
+def test_block_m_boundaries_and_ragged_counts(small, tokens):
+    """Token counts on both sides of the block-M switches (16 -> 32 -> 64 ...)
+    with ragged per-expert counts, and the empty call."""
+    xq, xsf, idx, w = O.make_tokens(tokens, small.h, small.e, small.k, seed=7 + tokens)
+    gen = parity(small) & 1
+    y = small.run(xq, xsf, idx, w)
+    ref = small.oracle(xq, xsf, idx, w)
+    check_dispatch_products(small.products(tokens, gen), ref.dispatch[0], small.block_m(tokens))
+    assert y.shape == (tokens, small.h)
+    if tokens:
+        assert_close(y, ref.y[0])
+
+
+def test_invalid_routes_are_skipped(small):
+    xq, xsf, idx, w = O.make_tokens(40, small.h, small.e, small.k, seed=3)
+    idx[::3, 0] = -1                 # "no route"
+    idx[1::5, 1] = small.e + 5       # out of range
+    idx[7] = -1                      # a token without any valid route
+    gen = parity(small) & 1
+    y = small.run(xq, xsf, idx, w)
+    ref = small.oracle(xq, xsf, idx, w)
+    check_dispatch_products(small.products(40, gen), ref.dispatch[0], small.block_m(40))
+    assert_close(y, ref.y[0])
+    assert torch.equal(y[7], torch.zeros_like(y[7]))
+
+
+def test_all_routes_invalid_gives_zeros(small):
+    xq, xsf, idx, w = O.make_tokens(12, small.h, small.e, small.k, seed=4)
+    idx[:] = -1
+    y = small.run(xq, xsf, idx, w)
+    assert torch.equal(y, torch.zeros_like(y))
+
+
+def test_hot_expert_spans_many_blocks(small):
+    """All routes to two experts: several M-blocks per expert, the others empty."""
+    tokens = 300
+    xq, xsf, idx, w = O.make_tokens(tokens, small.h, small.e, small.k, seed=5)
+    idx[:, 0], idx[:, 1] = 2, 5
+    gen = parity(small) & 1
+    y = small.run(xq, xsf, idx, w)
+    ref = small.oracle(xq, xsf, idx, w)
+    check_dispatch_products(small.products(tokens, gen), ref.dispatch[0], small.block_m(tokens))
+    assert_close(y, ref.y[0])
+
+
+def test_zero_route_weights_give_exact_zeros(small):
+    xq, xsf, idx, w = O.make_tokens(9, small.h, small.e, small.k, seed=6)
+    y = small.run(xq, xsf, idx, torch.zeros_like(w))
+    assert torch.equal(y, torch.zeros_like(y))
+
+
+def test_repeat_is_bitwise_identical_and_stats_accumulate(small):
+    xq, xsf, idx, w = O.make_tokens(33, small.h, small.e, small.k, seed=8)
+    stats = torch.zeros(small.e, dtype=torch.int32, device='cuda')
+    y1 = small.run(xq, xsf, idx, w, stats=stats)
+    y2 = small.run(xq, xsf, idx, w, stats=stats)
+    assert torch.equal(y1.view(torch.int16), y2.view(torch.int16))
+    expect = np.bincount(idx.numpy().reshape(-1), minlength=small.e)
+    assert np.array_equal(stats.cpu().numpy(), 2 * expect)
+
+
+def test_no_clamp_and_exact_math_paths(small):
+    xq, xsf, idx, w = O.make_tokens(20, small.h, small.e, small.k, seed=9)
+    for clamp, fast in ((None, True), (None, False), (0.5, False)):
+        y = small.run(xq, xsf, idx, w, clamp=clamp, fast_math=fast)
+        assert_close(y, small.oracle(xq, xsf, idx, w, clamp=clamp).y[0])
+
+
+def test_graph_replay_alternating_inputs(small):
+    """Readiness protocol of the reference (tests/test_gc_moe_readiness.py):
+    capture once, then replay with inputs A and B alternating at fixed
+    addresses; every replay must reproduce its own eager result."""
+    tokens = 24
+    a = O.make_tokens(tokens, small.h, small.e, small.k, seed=10)
+    b = O.make_tokens(tokens, small.h, small.e, small.k, seed=11)
+    y = torch.empty((tokens, small.h), dtype=torch.bfloat16, device='cuda')
+    eager = []
+    for inp in (a, b):
+        eager.append(small.run(*inp, y=y).clone())
+    assert not torch.equal(eager[0], eager[1])
+    import gc_moe_b200 as G
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        G.fp8_fp4_gc_moe(y, small.l1, small.l2, small.buf, activation_clamp=10.0)   # warm
+        with torch.cuda.graph(graph, stream=side):
+            G.fp8_fp4_gc_moe(y, small.l1, small.l2, small.buf, activation_clamp=10.0)
+    torch.cuda.current_stream().wait_stream(side)
+    for it in range(20):
+        small.stage(*(a, b)[it & 1])
+        y.fill_(float('nan'))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y.cpu().view(torch.int16), eager[it & 1].view(torch.int16)), it
+    small.buf.raise_on_device_error()
+
+
+def test_contract_violations_raise_like_the_reference(small):
+    import gc_moe_b200 as G
+    y = torch.empty((4, small.h), dtype=torch.bfloat16, device='cuda')
+    with pytest.raises(ValueError):       # misaligned output
+        odd = torch.empty(4 * small.h + 1, dtype=torch.bfloat16, device='cuda')[1:].view(4, small.h)
+        G.fp8_fp4_gc_moe(odd, small.l1, small.l2, small.buf)
+    with pytest.raises(ValueError):       # untransformed weights
+        G.fp8_fp4_gc_moe(y, (small.q1.to('cuda'), small.l1[1]), small.l2, small.buf)
+    with pytest.raises(ValueError):       # wrong dtype
+        G.fp8_fp4_gc_moe(y.float(), small.l1, small.l2, small.buf)
+    with pytest.raises(ValueError):       # stats of the wrong length
+        G.fp8_fp4_gc_moe(y, small.l1, small.l2, small.buf,
+                         cumulative_local_expert_recv_stats=torch.zeros(3, dtype=torch.int32, device='cuda'))
+    with pytest.raises(ValueError):
+        G.fp8_fp4_gc_moe(torch.empty((4000, small.h), dtype=torch.bfloat16, device='cuda'), small.l1, small.l2, small.buf)
