@@ -227,8 +227,10 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     const uint32_t stages = gemm_pick_stages(bm, sfbm, EL);
     if (stages < 2) return bail(fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm));
     plan->gemm_smem = gemm_smem_layout(stages, bm, sfbm, EL).total + 1024;
-    const uint32_t tmem_cols = pow2_at_least(2 * bm + 4 + sfbm / 32);
-    if (tmem_cols > 512) return bail(fail(GCMOE_ERR_UNSUPPORTED, "TMEM budget exceeded"));
+    // Two MMA-issuing warps while the accumulators of both fit TMEM and K splits evenly.
+    auto mma_warps_for = [&](uint32_t k) -> uint32_t {
+        return (bm <= 96 && (k / 128) % 2 == 0) ? 2u : 1u;
+    };
 
     auto fill_common = [&](GemmParams& g, uint32_t w_rows, uint32_t k) {
         memset(&g, 0, sizeof(g));
@@ -245,7 +247,8 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.local_experts = EL;
         g.weight_format = 5;
         g.weight_tx_bytes = 128 * 128 / 2;
-        g.tmem_cols = tmem_cols;
+        g.mma_warps = mma_warps_for(k);
+        g.tmem_cols = pow2_at_least(gemm_tmem_columns(bm, sfbm, g.mma_warps));
         g.act_sf_stride = q.sf_ring_tokens;
         g.capacity = q.capacity;
         g.hidden = H;

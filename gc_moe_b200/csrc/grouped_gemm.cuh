@@ -5,12 +5,21 @@
 // per pool block (BM tokens of one local expert) and 128-row weight tile.
 // Weights are the MMA's A operand (M = 128), tokens its B operand (N = BM,
 // a multiple of 16), so decode-sized token counts waste no tensor rows and the
-// HBM stream is the weight stream.  Roles (192 threads):
-//   warp 0    one lane issues the TMA / bulk loads of every K128 stage
-//   warp 1    one lane copies the stage's scale words to TMEM and issues the
-//             four K32 tcgen05.mma of the stage; owns the TMEM allocation
-//   warps 2-5 epilogue: read the FP32 accumulator from TMEM (each warp its own
+// HBM stream is the weight stream.  Roles (256 threads):
+//   warp 0    weight producer: per K128 stage one TMA tile (FP4 unpacked to
+//             8-bit containers on the fly) + one bulk copy of its scale words
+//   warp 2    activation producer: the stage's token tile + scale words
+//   warp 1,3  MMA issuers.  With decode-sized N a tcgen05.mma does so little
+//             work that the issue rate of ONE thread, not HBM, bounds the
+//             kernel; so the K loop is split between two issuing warps (even /
+//             odd stages), each with its own TMEM accumulator and scale
+//             columns, and the epilogue adds the two partial sums.  Warp 1
+//             owns the TMEM allocation.
+//   warp 4-7  epilogue: read the FP32 accumulators from TMEM (each warp its own
 //             32-lane quarter), fuse the layer's element-wise tail, store
+// Every async instruction is issued under elect.sync by a converged warp: the
+// compiler then feeds TMA / tcgen05 operands from uniform registers, which
+// measured 1.5x faster than the same code under `lane == 0`.
 // Two accumulator stages let the epilogue of tile i overlap the main loop of
 // tile i+1.  The work list is static: tile t = pool_block * n_tiles + n_tile,
 // CTA c takes t = c, c + grid, ... so the CTAs that share a pool block run at
@@ -29,12 +38,13 @@
 
 namespace gcmoe {
 
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 256;
 constexpr int kTileRows = 128;             // weight rows per tile = MMA M
 constexpr int kTileK = 128;                // K per pipeline stage = 4 MMAs of K32
 constexpr int kWeightStageBytes = 128 * 128;  // FP4 is unpacked to 8-bit containers by the TMA
 constexpr int kSfChunkBytes = 512;         // 128 rows x one packed int32 of four UE8M0 bytes
 constexpr int kMaxStages = 16;
+constexpr int kMaxBlockM = 240;
 constexpr int kSmemLimit = 232448;         // opt-in dynamic shared memory per CTA on sm_100
 
 enum GemmPhase : int { kPhaseL1 = 0, kPhaseL2 = 1, kPhaseRaw = 2 };
@@ -57,6 +67,7 @@ struct GemmParams {
     uint32_t block_m;        // BM
     uint32_t sf_block_m;     // BM rounded up to 128 (scale rows reserved per pool block)
     uint32_t stages;
+    uint32_t mma_warps;      // 1, or 2 = K loop split over two issuing warps
     uint32_t local_experts;
     uint32_t weight_format;  // 5 = e2m1 (FP4), 0 = e4m3
     uint32_t weight_tx_bytes;  // bytes the weight tile's TMA reports to the stage barrier
@@ -80,7 +91,7 @@ struct GemmParams {
 };
 
 struct GemmSmemLayout {
-    uint32_t w, a, sfw, sfa, bars, tables, amax, total;
+    uint32_t w, a, sfw, sfa, bars, tables, amax, rows, total;
 };
 
 __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint32_t block_m,
@@ -92,11 +103,12 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
     l.sfw = l.a + stages * block_m * kTileK;
     l.sfa = l.sfw + stages * kSfChunkBytes;
     l.bars = l.sfa + stages * sf_block_m * 4;
-    // full[stages], empty[stages], acc_full[2], acc_empty[2], drain, then the
+    // full[stages], empty[stages], acc_full[2], acc_empty[2], drain[2], then the
     // TMEM base slot and the abort word
-    l.tables = l.bars + (2 * stages + 5) * 8 + 16;
+    l.tables = l.bars + (2 * stages + 6) * 8 + 16;
     l.amax = l.tables + round_up_u32((2 * local_experts + 1) * 4, 16);
-    l.total = l.amax + 2 * 4 * 16 * 4;
+    l.rows = l.amax + 2 * 4 * 16 * 4;                 // amax exchange [2][4][16] floats
+    l.total = l.rows + 2 * block_m * 16;              // per-block row info, double buffered
     return l;
 }
 
@@ -107,6 +119,14 @@ __host__ inline uint32_t gemm_pick_stages(uint32_t block_m, uint32_t sf_block_m,
             return s;
     }
     return 0;
+}
+
+// TMEM columns: per accumulator stage one FP32 accumulator of BM columns per
+// issuing warp, then per issuing warp 4 columns of weight scales and
+// sf_block_m / 32 columns of activation scales.
+__host__ __device__ inline uint32_t gemm_tmem_columns(uint32_t block_m, uint32_t sf_block_m,
+                                                      uint32_t mma_warps) {
+    return 2 * mma_warps * block_m + mma_warps * (4 + sf_block_m / 32);
 }
 
 // SwiGLU in the reference's op order (impls:122-171): BF16-round the two
@@ -148,6 +168,18 @@ __device__ __forceinline__ bool all_epilogue_threads(bool pred) {
         : "memory");
     return all != 0;
 }
+__device__ __forceinline__ void epilogue_barrier() {
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// Position in the stage ring after `steps` more stages.
+struct StageCursor {
+    uint32_t stage = 0, phase = 0;
+    __device__ __forceinline__ void advance(uint32_t steps, uint32_t stages) {
+        stage += steps;
+        while (stage >= stages) { stage -= stages; phase ^= 1u; }
+    }
+};
 
 template <int kPhase>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -163,14 +195,16 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t bar_acc_full = bar_empty + p.stages * 8;
     const uint32_t bar_acc_empty = bar_acc_full + 16;
     const uint32_t bar_drain = bar_acc_empty + 16;
-    volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L.bars + (2 * p.stages + 5) * 8);
+    volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L.bars + (2 * p.stages + 6) * 8);
     volatile uint32_t* const abort_word = tmem_slot + 1;
     int* const tbl_start = reinterpret_cast<int*>(gbase + L.tables);      // [E_loc + 1]
     int* const tbl_count = tbl_start + p.local_experts + 1;               // [E_loc]
     float* const amax_x = reinterpret_cast<float*>(gbase + L.amax);       // [2][4][16]
+    uint32_t* const row_info = reinterpret_cast<uint32_t*>(gbase + L.rows);  // [2][BM][4]
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
+    const uint32_t mw = p.mma_warps;
 
     WaitCtl ctl;
     ctl.status = p.status;
@@ -180,14 +214,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
-            ptx::mbar_init(bar_full + 8 * s, 1);
-            ptx::mbar_init(bar_empty + 8 * s, 1);
+            ptx::mbar_init(bar_full + 8 * s, 2);    // weight producer + activation producer
+            ptx::mbar_init(bar_empty + 8 * s, 1);   // the commit of the MMA warp that read it
         }
         for (uint32_t i = 0; i < 2; ++i) {
-            ptx::mbar_init(bar_acc_full + 8 * i, 1);
+            ptx::mbar_init(bar_acc_full + 8 * i, mw);
             ptx::mbar_init(bar_acc_empty + 8 * i, 4);   // one arrival per epilogue warp
+            ptx::mbar_init(bar_drain + 8 * i, 1);
         }
-        ptx::mbar_init(bar_drain, 1);
         *abort_word = 0;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&p.tm_act);
@@ -224,57 +258,67 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         return left < bm ? left : bm;
     };
 
-    if (warp == 0) {
-        // ------------------------------------------------------------ loads
-        if (lane == 0) {
-            const uint32_t tx = p.weight_tx_bytes + kSfChunkBytes + bm * kTileK + p.sf_block_m * 4;
-            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
-            bool ok = true;
-            for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const uint32_t b = tile / p.n_tiles, nt = tile - b * p.n_tiles;
-                const uint32_t e = expert_of_block(b);
-                const uint32_t* wsf = p.w_sf + static_cast<size_t>(e) * p.k_blocks * p.w_sf_stride + nt * kTileRows;
-                const uint32_t* asf = p.act_sf + static_cast<size_t>(b) * p.sf_block_m;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, ctl, 1)) { ok = false; break; }
-                    const uint32_t full = bar_full + 8 * stage;
+    if (warp == 0 || warp == 2) {
+        // ------------------------------------------------------------ producers
+        const bool weights = warp == 0;
+        const uint32_t tx = weights ? p.weight_tx_bytes + kSfChunkBytes : bm * kTileK + p.sf_block_m * 4;
+        StageCursor cur;
+        uint32_t armed = 0, armed_parity = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+            const uint32_t b = tile / p.n_tiles, nt = tile - b * p.n_tiles;
+            const uint32_t e = expert_of_block(b);
+            const uint32_t* wsf = p.w_sf + static_cast<size_t>(e) * p.k_blocks * p.w_sf_stride + nt * kTileRows;
+            const uint32_t* asf = p.act_sf + static_cast<size_t>(b) * p.sf_block_m;
+            for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                if (!mbar_wait(bar_empty + 8 * cur.stage, cur.phase ^ 1u, ctl, 1)) { ok = false; break; }
+                const uint32_t full = bar_full + 8 * cur.stage;
+                armed |= 1u << cur.stage;
+                armed_parity = (armed_parity & ~(1u << cur.stage)) | (cur.phase << cur.stage);
+                if (ptx::elect_one()) {
                     ptx::mbar_arrive_expect_tx(full, tx);
-                    armed |= 1u << stage;
-                    armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-                    if (p.weight_format == 5u)
-                        ptx::tma_load_4d(base + L.w + stage * kWeightStageBytes, &p.tm_w, full, 0,
-                                         nt * kTileRows, kb, e, ptx::kEvictFirst);
-                    else
-                        ptx::tma_load_3d(base + L.w + stage * kWeightStageBytes, &p.tm_w, full, 0,
-                                         nt * kTileRows, kb, ptx::kEvictFirst);
-                    ptx::bulk_load_1d(base + L.sfw + stage * kSfChunkBytes,
-                                      wsf + static_cast<size_t>(kb) * p.w_sf_stride, kSfChunkBytes,
-                                      full, ptx::kEvictFirst);
-                    ptx::tma_load_2d(base + L.a + stage * bm * kTileK, &p.tm_act, full, kb * kTileK,
-                                     b * bm, ptx::kEvictLast);
-                    ptx::bulk_load_1d(base + L.sfa + stage * p.sf_block_m * 4,
-                                      asf + static_cast<size_t>(kb) * p.act_sf_stride,
-                                      p.sf_block_m * 4, full, ptx::kEvictLast);
-                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                    if (weights) {
+                        if (p.weight_format == 5u)
+                            ptx::tma_load_4d(base + L.w + cur.stage * kWeightStageBytes, &p.tm_w, full, 0,
+                                             nt * kTileRows, kb, e, ptx::kEvictFirst);
+                        else
+                            ptx::tma_load_3d(base + L.w + cur.stage * kWeightStageBytes, &p.tm_w, full, 0,
+                                             nt * kTileRows, kb, ptx::kEvictFirst);
+                        ptx::bulk_load_1d(base + L.sfw + cur.stage * kSfChunkBytes,
+                                          wsf + static_cast<size_t>(kb) * p.w_sf_stride, kSfChunkBytes,
+                                          full, ptx::kEvictFirst);
+                    } else {
+                        ptx::tma_load_2d(base + L.a + cur.stage * bm * kTileK, &p.tm_act, full, kb * kTileK,
+                                         b * bm, ptx::kEvictLast);
+                        ptx::bulk_load_1d(base + L.sfa + cur.stage * p.sf_block_m * 4,
+                                          asf + static_cast<size_t>(kb) * p.act_sf_stride,
+                                          p.sf_block_m * 4, full, ptx::kEvictLast);
+                    }
                 }
-            }
-            if (!ok) {
-                // Another role gave up.  Let the copies already in flight land
-                // (they depend on nothing) before the CTA releases its memory.
-                const uint64_t t0 = ptx::globaltimer_ns();
-                for (uint32_t s = 0; s < p.stages; ++s) {
-                    if (!(armed >> s & 1u)) continue;
-                    while (!ptx::mbar_try_wait(bar_full + 8 * s, (armed_parity >> s) & 1u) &&
-                           ptx::globaltimer_ns() - t0 < 2000000ull) {}
-                }
+                __syncwarp();
+                cur.advance(1, p.stages);
             }
         }
-    } else if (warp == 1) {
+        if (!ok && lane == 0) {
+            // Another role gave up.  Let the copies already in flight land (they
+            // depend on nothing) before the CTA releases its shared memory.
+            const uint64_t t0 = ptx::globaltimer_ns();
+            for (uint32_t s = 0; s < p.stages; ++s) {
+                if (!(armed >> s & 1u)) continue;
+                while (!ptx::mbar_try_wait(bar_full + 8 * s, (armed_parity >> s) & 1u) &&
+                       ptx::globaltimer_ns() - t0 < 2000000ull) {}
+            }
+        }
+    } else if (warp == 1 || warp == 3) {
         // ------------------------------------------------------------ MMA issue
-        if (lane == 0) {
-            const uint32_t sfw_tmem = tmem_base + 2 * bm;        // 4 columns
-            const uint32_t sfa_tmem = sfw_tmem + 4;              // sf_block_m / 32 columns
-            uint32_t stage = 0, phase = 0, it = 0;
+        const uint32_t m = warp >> 1;            // 0 or 1: which half of the K loop
+        if (m < mw) {
+            const uint32_t sf_cols = 4 + p.sf_block_m / 32;
+            const uint32_t sfw_tmem = tmem_base + 2 * mw * bm + m * sf_cols;   // 4 columns
+            const uint32_t sfa_tmem = sfw_tmem + 4;                            // sf_block_m / 32 columns
+            StageCursor cur;
+            cur.advance(m, p.stages);
+            uint32_t it = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
                 const uint32_t b = tile / p.n_tiles;
@@ -284,36 +328,39 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 const uint32_t as = it & 1u;
                 if (!mbar_wait(bar_acc_empty + 8 * as, ((it >> 1) & 1u) ^ 1u, ctl, 2)) { ok = false; break; }
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + as * bm;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait(bar_full + 8 * stage, phase, ctl, 3)) { ok = false; break; }
+                const uint32_t d_tmem = tmem_base + (as * mw + m) * bm;
+                for (uint32_t kb = m; kb < p.k_blocks; kb += mw) {
+                    if (!mbar_wait(bar_full + 8 * cur.stage, cur.phase, ctl, 3)) { ok = false; break; }
                     ptx::tc_fence_after();
-                    const uint32_t sfw_s = base + L.sfw + stage * kSfChunkBytes;
-                    const uint32_t sfa_s = base + L.sfa + stage * p.sf_block_m * 4;
-                    ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
-                    ptx::tmem_cp_sf(sfa_tmem, ptx::smem_desc(sfa_s, 128, false));
-                    if (p.sf_block_m > 128)
-                        ptx::tmem_cp_sf(sfa_tmem + 4, ptx::smem_desc(sfa_s + kSfChunkBytes, 128, false));
-                    const uint64_t wdesc = ptx::smem_desc(base + L.w + stage * kWeightStageBytes, 1024, true);
-                    const uint64_t adesc = ptx::smem_desc(base + L.a + stage * bm * kTileK, 1024, true);
+                    if (ptx::elect_one()) {
+                        const uint32_t sfw_s = base + L.sfw + cur.stage * kSfChunkBytes;
+                        const uint32_t sfa_s = base + L.sfa + cur.stage * p.sf_block_m * 4;
+                        ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
+                        ptx::tmem_cp_sf(sfa_tmem, ptx::smem_desc(sfa_s, 128, false));
+                        if (p.sf_block_m > 128)
+                            ptx::tmem_cp_sf(sfa_tmem + 4, ptx::smem_desc(sfa_s + kSfChunkBytes, 128, false));
+                        const uint64_t wdesc = ptx::smem_desc(base + L.w + cur.stage * kWeightStageBytes, 1024, true);
+                        const uint64_t adesc = ptx::smem_desc(base + L.a + cur.stage * bm * kTileK, 1024, true);
 #pragma unroll
-                    for (uint32_t k = 0; k < 4; ++k) {
-                        // 32 K elements = 32 bytes in the swizzled row = +2 in 16-byte units;
-                        // scale byte k of the stage's packed word for both operands.
-                        ptx::mma_mxf8f6f4(d_tmem, wdesc + 2 * k, adesc + 2 * k,
-                                          idesc | (k << 29) | (k << 4), sfw_tmem, sfa_tmem,
-                                          (kb | k) != 0u);
+                        for (uint32_t k = 0; k < 4; ++k) {
+                            // 32 K elements = 32 bytes in the swizzled row = +2 in 16-byte units;
+                            // scale byte k of the stage's packed word for both operands.
+                            ptx::mma_mxf8f6f4(d_tmem, wdesc + 2 * k, adesc + 2 * k,
+                                              idesc | (k << 29) | (k << 4), sfw_tmem, sfa_tmem,
+                                              (kb != m || k != 0u) ? 1u : 0u);
+                        }
+                        ptx::tc_commit(bar_empty + 8 * cur.stage);
+                        if (kb + mw >= p.k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
                     }
-                    ptx::tc_commit(bar_empty + 8 * stage);
-                    if (kb + 1 == p.k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
-                    if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+                    __syncwarp();
+                    cur.advance(mw, p.stages);
                 }
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 // Do not free TMEM under MMAs that may still be running.
-                ptx::tc_commit(bar_drain);
+                ptx::tc_commit(bar_drain + 8 * m);
                 const uint64_t t0 = ptx::globaltimer_ns();
-                while (!ptx::mbar_try_wait(bar_drain, 0) && ptx::globaltimer_ns() - t0 < 2000000ull) {}
+                while (!ptx::mbar_try_wait(bar_drain + 8 * m, 0) && ptx::globaltimer_ns() - t0 < 2000000ull) {}
             }
         }
     } else {
@@ -321,6 +368,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t q = warp & 3u;           // the TMEM lane quarter this warp can read
         const uint32_t r = q * 32 + lane;       // weight row inside the tile
         const uint32_t lane_base = (q * 32) << 16;
+        const uint32_t etid = threadIdx.x - 128;
         uint32_t it = 0;
         uint32_t xbuf = 0;
         bool ok = true;
@@ -332,7 +380,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t ncols = round_up_u32(valid, 16);
             const uint32_t as = it & 1u;
             const uint32_t row0 = b * bm;       // pool row of accumulator column 0
-            // Every epilogue thread must take the same exit, or the named barrier
+            // Stage what the stores need to know about the block's rows while the
+            // main loop is still running: route weight (gate/up) or destination.
+            uint32_t* const info = row_info + (it & 1u) * bm * 4;
+            if constexpr (kPhase == kPhaseL1) {
+                for (uint32_t i = etid; i < valid; i += 128)
+                    info[i] = __float_as_uint(p.route_weight[row0 + i]);
+            } else if constexpr (kPhase == kPhaseL2) {
+                for (uint32_t i = etid; i < valid * 3; i += 128)
+                    info[i] = p.metadata[static_cast<size_t>(row0) * 3 + i];
+            }
+            // Every epilogue thread must take the same exit, or the named barriers
             // below would wait for threads that have left: vote on the outcome.
             if (!all_epilogue_threads(mbar_wait(bar_acc_full + 8 * as, (it >> 1) & 1u, ctl, 4))) {
                 ok = false;
@@ -341,10 +399,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             ptx::tc_fence_after();
             for (uint32_t c0 = 0; c0 < ncols; c0 += 16) {
                 uint32_t vi[16];
-                ptx::tmem_ld16(tmem_base + lane_base + as * bm + c0, vi);
-                ptx::tmem_ld_wait();
+                ptx::tmem_ld16(tmem_base + lane_base + (as * mw) * bm + c0, vi);
+                if (mw == 2) {
+                    uint32_t vj[16];
+                    ptx::tmem_ld16(tmem_base + lane_base + (as * mw + 1) * bm + c0, vj);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (uint32_t c = 0; c < 16; ++c)
+                        vi[c] = __float_as_uint(__fadd_rn(__uint_as_float(vi[c]), __uint_as_float(vj[c])));
+                } else {
+                    ptx::tmem_ld_wait();
+                }
                 if (c0 + 16 >= ncols) {
-                    // Last read of this accumulator stage: hand it back to the MMA warp.
+                    // Last read of this accumulator stage: hand it back to the MMA warps.
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(bar_acc_empty + 8 * as);
@@ -362,8 +429,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     for (uint32_t c = 0; c < 16; ++c) {
                         const uint32_t col = c0 + c;
                         if (col < valid) {
-                            const uint32_t* m = p.metadata + static_cast<size_t>(row0 + col) * 3;
-                            const uint32_t src_rank = m[0], src_token = m[1], slot = m[2];
+                            const uint32_t src_rank = info[col * 3], src_token = info[col * 3 + 1], slot = info[col * 3 + 2];
                             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.combine_base[src_rank]) +
                                 (static_cast<size_t>(slot) * p.capacity + src_token) * p.hidden +
                                 nt * kTileRows + r;
@@ -384,7 +450,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         const float g = is_up ? recv : even;
                         const float u = is_up ? odd : recv;
                         const uint32_t col = c0 + 2 * j + is_up;
-                        const float w = col < valid ? p.route_weight[row0 + col] : 0.0f;
+                        const float w = col < valid ? __uint_as_float(info[col]) : 0.0f;
                         res[j] = swiglu_weighted(g, u, w, clamp_bf16, p.has_clamp != 0, p.fast_math != 0);
                         float a = fabsf(res[j]);
                         a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
@@ -400,12 +466,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 #pragma unroll
                         for (uint32_t j = 0; j < 8; ++j) mine[2 * j + is_up] = amax[j];
                     }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    epilogue_barrier();
 #pragma unroll
                     for (uint32_t j = 0; j < 8; ++j) {
                         const uint32_t col = c0 + 2 * j + is_up;
-                        const float m = fmaxf(amax[j], other[2 * j + is_up]);
-                        const uint32_t code = ue8m0_scale_byte(m);
+                        const float mx = fmaxf(amax[j], other[2 * j + is_up]);
+                        const uint32_t code = ue8m0_scale_byte(mx);
                         const float inv = __uint_as_float((254u - code) << 23);
                         const uint32_t byte = ptx::cvt_e4m3x2(__fmul_rn(res[j], inv), 0.0f) & 0xFFu;
                         if (col < valid) {

@@ -24,6 +24,17 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
+// True in exactly one lane of a converged warp.  Unlike `lane == 0`, the
+// compiler knows the guarded code runs in a single thread and can feed the
+// TMA / tcgen05 instructions from uniform registers directly.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
