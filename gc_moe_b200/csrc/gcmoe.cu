@@ -227,10 +227,10 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     const uint32_t stages = gemm_pick_stages(bm, sfbm, EL);
     if (stages < 2) return bail(fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm));
     plan->gemm_smem = gemm_smem_layout(stages, bm, sfbm, EL).total + 1024;
-    // Two MMA-issuing warps while the accumulators of both fit TMEM and K splits evenly.
-    auto mma_warps_for = [&](uint32_t k) -> uint32_t {
-        return (bm <= 96 && (k / 128) % 2 == 0) ? 2u : 1u;
-    };
+    // Two accumulator stages (epilogue overlaps the next tile) while they fit TMEM.
+    const uint32_t acc_stages = gemm_tmem_columns(bm, sfbm, 2) <= 512 ? 2u : 1u;
+    if (gemm_tmem_columns(bm, sfbm, acc_stages) > 512)
+        return bail(fail(GCMOE_ERR_UNSUPPORTED, "TMEM budget exceeded"));
 
     auto fill_common = [&](GemmParams& g, uint32_t w_rows, uint32_t k) {
         memset(&g, 0, sizeof(g));
@@ -240,15 +240,15 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.timeout_ns = timeout_ns;
         g.w_rows = w_rows;
         g.k_blocks = k / 128;
-        g.n_tiles = w_rows / 128;
+        g.n_tiles = w_rows / kTileRows;
         g.block_m = bm;
         g.sf_block_m = sfbm;
         g.stages = stages;
         g.local_experts = EL;
         g.weight_format = 5;
-        g.weight_tx_bytes = 128 * 128 / 2;
-        g.mma_warps = mma_warps_for(k);
-        g.tmem_cols = pow2_at_least(gemm_tmem_columns(bm, sfbm, g.mma_warps));
+        g.weight_tx_bytes = kTileRows * 128 / 2;
+        g.acc_stages = acc_stages;
+        g.tmem_cols = pow2_at_least(gemm_tmem_columns(bm, sfbm, acc_stages));
         g.act_sf_stride = q.sf_ring_tokens;
         g.capacity = q.capacity;
         g.hidden = H;
@@ -262,10 +262,10 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         if (int rc = encode_map(&g.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
             return rc;
         // FP4 weights: 128-element (64-byte) rows of one K128 tile are adjacent,
-        // so a 128 x 128 box is one contiguous 8 KiB range in HBM.
+        // so a 128 x 256 box is one contiguous 16 KiB range in HBM.
         const uint64_t wdims[4] = {128, w_rows, k / 128, EL};
         const uint64_t wstr[3] = {64, uint64_t(w_rows) * 64, uint64_t(w_rows) * 64 * (k / 128)};
-        const uint32_t wbox[4] = {128, 128, 1, 1};
+        const uint32_t wbox[4] = {128, kTileRows, 1, 1};
         return encode_map(&g.tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, weights, wdims, wstr, wbox, what);
     };
 
@@ -361,6 +361,20 @@ extern "C" int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* 
                     words[kStatusCode], words[kStatusKernel], words[kStatusSite], words[kStatusBlock],
                     words[kStatusObserved], words[kStatusExpected]);
     return GCMOE_OK;
+}
+
+extern "C" int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cuda_stream) {
+    if (plan == nullptr || out == 0 || which < 0 || which > 1) return fail(GCMOE_ERR_INVALID, "bad argument");
+    GemmParams g = which == 0 ? plan->l1 : plan->l2;
+    g.timing = reinterpret_cast<unsigned long long*>(out);
+    const uint32_t grid = which == 0 ? plan->gemm_grid_l1 : plan->gemm_grid_l2;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    if (which == 0)
+        grouped_gemm_kernel<kPhaseL1><<<grid, kGemmThreads, plan->gemm_smem, s>>>(g);
+    else
+        grouped_gemm_kernel<kPhaseL2><<<grid, kGemmThreads, plan->gemm_smem, s>>>(g);
+    GCMOE_CUDA(cudaGetLastError());
+    return int(grid);
 }
 
 extern "C" int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream) {

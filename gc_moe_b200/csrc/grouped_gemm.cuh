@@ -2,19 +2,22 @@
 //
 //   out[weight_row, token] = sum_k W[e][weight_row, k] * X[token, k]
 //
-// per pool block (BM tokens of one local expert) and 128-row weight tile.
-// Weights are the MMA's A operand (M = 128), tokens its B operand (N = BM,
-// a multiple of 16), so decode-sized token counts waste no tensor rows and the
-// HBM stream is the weight stream.  Roles (256 threads):
-//   warp 0    weight producer: per K128 stage one TMA tile (FP4 unpacked to
-//             8-bit containers on the fly) + one bulk copy of its scale words
+// per pool block (BM tokens of one local expert) and 256-row weight tile.
+// Weights are the MMA's A operand (two M = 128 halves per tile), tokens its B
+// operand (N = BM, a multiple of 16), so decode-sized token counts waste no
+// tensor rows and the HBM stream is the weight stream.  Roles (256 threads):
+//   warp 0    weight producer: per K128 stage one TMA tile of 256 rows (16 KiB
+//             of packed FP4, unpacked to 8-bit containers on the fly) + one
+//             bulk copy of its scale words
 //   warp 2    activation producer: the stage's token tile + scale words
-//   warp 1,3  MMA issuers.  With decode-sized N a tcgen05.mma does so little
-//             work that the issue rate of ONE thread, not HBM, bounds the
-//             kernel; so the K loop is split between two issuing warps (even /
-//             odd stages), each with its own TMEM accumulator and scale
-//             columns, and the epilogue adds the two partial sums.  Warp 1
-//             owns the TMEM allocation.
+//   warp 1,3  MMA issuers, one per 128-row half of the tile, each with its own
+//             TMEM accumulator and scale columns.  With decode-sized N a
+//             tcgen05.mma does so little work that instruction issue, not HBM,
+//             bounds the kernel: a copy instruction costs the SM about 65 ns
+//             and the MMA sequence of a stage about 290 ns of its issuing
+//             thread (measured), so a stage carries 17 KiB for four copies and
+//             the two halves are issued in parallel.  Warp 1 owns the TMEM
+//             allocation.
 //   warp 4-7  epilogue: read the FP32 accumulators from TMEM (each warp its own
 //             32-lane quarter), fuse the layer's element-wise tail, store
 // Every async instruction is issued under elect.sync by a converged warp: the
@@ -39,10 +42,13 @@
 namespace gcmoe {
 
 constexpr int kGemmThreads = 256;
-constexpr int kTileRows = 128;             // weight rows per tile = MMA M
+constexpr int kHalfRows = 128;             // MMA M: rows of one accumulator
+constexpr int kTileRows = 256;             // weight rows per tile (two halves)
 constexpr int kTileK = 128;                // K per pipeline stage = 4 MMAs of K32
-constexpr int kWeightStageBytes = 128 * 128;  // FP4 is unpacked to 8-bit containers by the TMA
+constexpr int kHalfStageBytes = 128 * 128;   // FP4 is unpacked to 8-bit containers by the TMA
+constexpr int kWeightStageBytes = 2 * kHalfStageBytes;
 constexpr int kSfChunkBytes = 512;         // 128 rows x one packed int32 of four UE8M0 bytes
+constexpr int kWeightSfStageBytes = 2 * kSfChunkBytes;
 constexpr int kMaxStages = 16;
 constexpr int kMaxBlockM = 240;
 constexpr int kSmemLimit = 232448;         // opt-in dynamic shared memory per CTA on sm_100
@@ -51,7 +57,7 @@ enum GemmPhase : int { kPhaseL1 = 0, kPhaseL2 = 1, kPhaseRaw = 2 };
 
 struct GemmParams {
     CUtensorMap tm_act;     // u8 [rows][K], box 128 x BM, 128-byte swizzle
-    CUtensorMap tm_w;       // FP4: 16U4_ALIGN16B [E][K/128][rows][128], box 128 x 128
+    CUtensorMap tm_w;       // FP4: 16U4_ALIGN16B [E][K/128][rows][128], box 128 x 256
                             // FP8: u8 [K/128][rows][128]
     const uint32_t* act_sf;  // packed scale words, MN-major: word (kb, r) at kb * act_sf_stride + r
     const uint32_t* w_sf;    // word (e, kb, row) at (e * k_blocks + kb) * w_sf_stride + row
@@ -63,11 +69,11 @@ struct GemmParams {
     uint32_t w_sf_stride;    // words between consecutive K128 planes of w_sf
     uint32_t w_rows;         // weight rows per expert (2I for the gate/up GEMM, H for the down GEMM)
     uint32_t k_blocks;       // K / 128
-    uint32_t n_tiles;        // w_rows / 128
+    uint32_t n_tiles;        // w_rows / 256
     uint32_t block_m;        // BM
     uint32_t sf_block_m;     // BM rounded up to 128 (scale rows reserved per pool block)
     uint32_t stages;
-    uint32_t mma_warps;      // 1, or 2 = K loop split over two issuing warps
+    uint32_t acc_stages;     // 2, or 1 when two accumulator stages exceed TMEM
     uint32_t local_experts;
     uint32_t weight_format;  // 5 = e2m1 (FP4), 0 = e4m3
     uint32_t weight_tx_bytes;  // bytes the weight tile's TMA reports to the stage barrier
@@ -88,6 +94,30 @@ struct GemmParams {
     uint32_t hidden;
     // ---- raw epilogue (kPhaseRaw): FP32 accumulators, [rows][w_rows]
     float* raw_out;
+    // ---- optional role timing: [grid][kTimingRoles][kTimingWords] clock64 totals, or null
+    unsigned long long* timing;
+};
+
+// Role timing slots (per CTA): cycles inside the role loop, cycles spent in
+// each of the role's waits.  Roles: 0 weight producer, 1 activation producer,
+// 2 MMA warp 0, 3 MMA warp 1, 4 epilogue (warp 4).
+constexpr int kTimingRoles = 5;
+constexpr int kTimingWords = 4;   // total, wait A, wait B, tiles
+
+struct RoleTimer {
+    unsigned long long* slot;
+    long long begin, wait_a = 0, wait_b = 0, mark = 0;
+    __device__ __forceinline__ RoleTimer(unsigned long long* base, uint32_t role)
+        : slot(base ? base + (static_cast<size_t>(blockIdx.x) * kTimingRoles + role) * kTimingWords : nullptr),
+          begin(base ? ptx::clock_cycles() : 0) {}
+    __device__ __forceinline__ void start() { if (slot) mark = ptx::clock_cycles(); }
+    __device__ __forceinline__ void stop_a() { if (slot) wait_a += ptx::clock_cycles() - mark; }
+    __device__ __forceinline__ void stop_b() { if (slot) wait_b += ptx::clock_cycles() - mark; }
+    __device__ __forceinline__ void finish(uint32_t tiles) {
+        if (slot && (threadIdx.x & 31) == 0) {
+            slot[0] = ptx::clock_cycles() - begin; slot[1] = wait_a; slot[2] = wait_b; slot[3] = tiles;
+        }
+    }
 };
 
 struct GemmSmemLayout {
@@ -101,7 +131,7 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
     l.w = 0;
     l.a = l.w + stages * kWeightStageBytes;
     l.sfw = l.a + stages * block_m * kTileK;
-    l.sfa = l.sfw + stages * kSfChunkBytes;
+    l.sfa = l.sfw + stages * kWeightSfStageBytes;
     l.bars = l.sfa + stages * sf_block_m * 4;
     // full[stages], empty[stages], acc_full[2], acc_empty[2], drain[2], then the
     // TMEM base slot and the abort word
@@ -122,11 +152,11 @@ __host__ inline uint32_t gemm_pick_stages(uint32_t block_m, uint32_t sf_block_m,
 }
 
 // TMEM columns: per accumulator stage one FP32 accumulator of BM columns per
-// issuing warp, then per issuing warp 4 columns of weight scales and
-// sf_block_m / 32 columns of activation scales.
+// tile half, then per half 4 columns of weight scales and sf_block_m / 32
+// columns of activation scales.
 __host__ __device__ inline uint32_t gemm_tmem_columns(uint32_t block_m, uint32_t sf_block_m,
-                                                      uint32_t mma_warps) {
-    return 2 * mma_warps * block_m + mma_warps * (4 + sf_block_m / 32);
+                                                      uint32_t acc_stages) {
+    return acc_stages * 2 * block_m + 2 * (4 + sf_block_m / 32);
 }
 
 // SwiGLU in the reference's op order (impls:122-171): BF16-round the two
@@ -204,7 +234,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t mw = p.mma_warps;
 
     WaitCtl ctl;
     ctl.status = p.status;
@@ -215,10 +244,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
             ptx::mbar_init(bar_full + 8 * s, 2);    // weight producer + activation producer
-            ptx::mbar_init(bar_empty + 8 * s, 1);   // the commit of the MMA warp that read it
+            ptx::mbar_init(bar_empty + 8 * s, 2);   // the commits of the two MMA warps
         }
         for (uint32_t i = 0; i < 2; ++i) {
-            ptx::mbar_init(bar_acc_full + 8 * i, mw);
+            ptx::mbar_init(bar_acc_full + 8 * i, 2);
             ptx::mbar_init(bar_acc_empty + 8 * i, 4);   // one arrival per epilogue warp
             ptx::mbar_init(bar_drain + 8 * i, 1);
         }
@@ -261,17 +290,21 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     if (warp == 0 || warp == 2) {
         // ------------------------------------------------------------ producers
         const bool weights = warp == 0;
-        const uint32_t tx = weights ? p.weight_tx_bytes + kSfChunkBytes : bm * kTileK + p.sf_block_m * 4;
+        const uint32_t tx = weights ? p.weight_tx_bytes + kWeightSfStageBytes : bm * kTileK + p.sf_block_m * 4;
         StageCursor cur;
-        uint32_t armed = 0, armed_parity = 0;
+        uint32_t armed = 0, armed_parity = 0, ntiles = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        RoleTimer timer(p.timing, weights ? 0 : 1);
+        for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++ntiles) {
             const uint32_t b = tile / p.n_tiles, nt = tile - b * p.n_tiles;
             const uint32_t e = expert_of_block(b);
             const uint32_t* wsf = p.w_sf + static_cast<size_t>(e) * p.k_blocks * p.w_sf_stride + nt * kTileRows;
             const uint32_t* asf = p.act_sf + static_cast<size_t>(b) * p.sf_block_m;
             for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-                if (!mbar_wait(bar_empty + 8 * cur.stage, cur.phase ^ 1u, ctl, 1)) { ok = false; break; }
+                timer.start();
+                const bool got = mbar_wait(bar_empty + 8 * cur.stage, cur.phase ^ 1u, ctl, 1);
+                timer.stop_a();
+                if (!got) { ok = false; break; }
                 const uint32_t full = bar_full + 8 * cur.stage;
                 armed |= 1u << cur.stage;
                 armed_parity = (armed_parity & ~(1u << cur.stage)) | (cur.phase << cur.stage);
@@ -284,8 +317,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         else
                             ptx::tma_load_3d(base + L.w + cur.stage * kWeightStageBytes, &p.tm_w, full, 0,
                                              nt * kTileRows, kb, ptx::kEvictFirst);
-                        ptx::bulk_load_1d(base + L.sfw + cur.stage * kSfChunkBytes,
-                                          wsf + static_cast<size_t>(kb) * p.w_sf_stride, kSfChunkBytes,
+                        ptx::bulk_load_1d(base + L.sfw + cur.stage * kWeightSfStageBytes,
+                                          wsf + static_cast<size_t>(kb) * p.w_sf_stride, kWeightSfStageBytes,
                                           full, ptx::kEvictFirst);
                     } else {
                         ptx::tma_load_2d(base + L.a + cur.stage * bm * kTileK, &p.tm_act, full, kb * kTileK,
@@ -299,6 +332,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 cur.advance(1, p.stages);
             }
         }
+        timer.finish(ntiles);
         if (!ok && lane == 0) {
             // Another role gave up.  Let the copies already in flight land (they
             // depend on nothing) before the CTA releases its shared memory.
@@ -311,35 +345,42 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
     } else if (warp == 1 || warp == 3) {
         // ------------------------------------------------------------ MMA issue
-        const uint32_t m = warp >> 1;            // 0 or 1: which half of the K loop
-        if (m < mw) {
+        const uint32_t m = warp >> 1;            // 0 or 1: which 128-row half of the tile
+        {
             const uint32_t sf_cols = 4 + p.sf_block_m / 32;
-            const uint32_t sfw_tmem = tmem_base + 2 * mw * bm + m * sf_cols;   // 4 columns
+            const uint32_t sfw_tmem = tmem_base + p.acc_stages * 2 * bm + m * sf_cols;   // 4 columns
             const uint32_t sfa_tmem = sfw_tmem + 4;                            // sf_block_m / 32 columns
             StageCursor cur;
-            cur.advance(m, p.stages);
             uint32_t it = 0;
             bool ok = true;
+            RoleTimer timer(p.timing, 2 + m);
             for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
                 const uint32_t b = tile / p.n_tiles;
                 const uint32_t e = expert_of_block(b);
                 const uint32_t n = round_up_u32(valid_rows(b, e), 16);
                 const uint32_t idesc = ptx::instr_desc(n, p.weight_format);
-                const uint32_t as = it & 1u;
-                if (!mbar_wait(bar_acc_empty + 8 * as, ((it >> 1) & 1u) ^ 1u, ctl, 2)) { ok = false; break; }
+                const uint32_t as = p.acc_stages == 2 ? (it & 1u) : 0u;
+                const uint32_t acc_phase = p.acc_stages == 2 ? ((it >> 1) & 1u) : (it & 1u);
+                timer.start();
+                const bool acc_free = mbar_wait(bar_acc_empty + 8 * as, acc_phase ^ 1u, ctl, 2);
+                timer.stop_b();
+                if (!acc_free) { ok = false; break; }
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (as * mw + m) * bm;
-                for (uint32_t kb = m; kb < p.k_blocks; kb += mw) {
-                    if (!mbar_wait(bar_full + 8 * cur.stage, cur.phase, ctl, 3)) { ok = false; break; }
+                const uint32_t d_tmem = tmem_base + (as * 2 + m) * bm;
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    timer.start();
+                    const bool got = mbar_wait(bar_full + 8 * cur.stage, cur.phase, ctl, 3);
+                    timer.stop_a();
+                    if (!got) { ok = false; break; }
                     ptx::tc_fence_after();
                     if (ptx::elect_one()) {
-                        const uint32_t sfw_s = base + L.sfw + cur.stage * kSfChunkBytes;
+                        const uint32_t sfw_s = base + L.sfw + cur.stage * kWeightSfStageBytes + m * kSfChunkBytes;
                         const uint32_t sfa_s = base + L.sfa + cur.stage * p.sf_block_m * 4;
                         ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
                         ptx::tmem_cp_sf(sfa_tmem, ptx::smem_desc(sfa_s, 128, false));
                         if (p.sf_block_m > 128)
                             ptx::tmem_cp_sf(sfa_tmem + 4, ptx::smem_desc(sfa_s + kSfChunkBytes, 128, false));
-                        const uint64_t wdesc = ptx::smem_desc(base + L.w + cur.stage * kWeightStageBytes, 1024, true);
+                        const uint64_t wdesc = ptx::smem_desc(base + L.w + cur.stage * kWeightStageBytes + m * kHalfStageBytes, 1024, true);
                         const uint64_t adesc = ptx::smem_desc(base + L.a + cur.stage * bm * kTileK, 1024, true);
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k) {
@@ -347,15 +388,16 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                             // scale byte k of the stage's packed word for both operands.
                             ptx::mma_mxf8f6f4(d_tmem, wdesc + 2 * k, adesc + 2 * k,
                                               idesc | (k << 29) | (k << 4), sfw_tmem, sfa_tmem,
-                                              (kb != m || k != 0u) ? 1u : 0u);
+                                              (kb | k) != 0u ? 1u : 0u);
                         }
                         ptx::tc_commit(bar_empty + 8 * cur.stage);
-                        if (kb + mw >= p.k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
+                        if (kb + 1 == p.k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
                     }
                     __syncwarp();
-                    cur.advance(mw, p.stages);
+                    cur.advance(1, p.stages);
                 }
             }
+            timer.finish(it);
             if (!ok && lane == 0) {
                 // Do not free TMEM under MMAs that may still be running.
                 ptx::tc_commit(bar_drain + 8 * m);
@@ -373,12 +415,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         uint32_t xbuf = 0;
         bool ok = true;
         const float clamp_bf16 = __bfloat162float(__float2bfloat16_rn(p.clamp));
+        RoleTimer timer(warp == 4 ? p.timing : nullptr, 4);
         for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
             const uint32_t b = tile / p.n_tiles, nt = tile - b * p.n_tiles;
             const uint32_t e = expert_of_block(b);
             const uint32_t valid = valid_rows(b, e);
             const uint32_t ncols = round_up_u32(valid, 16);
-            const uint32_t as = it & 1u;
+            const uint32_t as = p.acc_stages == 2 ? (it & 1u) : 0u;
+            const uint32_t acc_phase = p.acc_stages == 2 ? ((it >> 1) & 1u) : (it & 1u);
             const uint32_t row0 = b * bm;       // pool row of accumulator column 0
             // Stage what the stores need to know about the block's rows while the
             // main loop is still running: route weight (gate/up) or destination.
@@ -392,25 +436,21 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
             // Every epilogue thread must take the same exit, or the named barriers
             // below would wait for threads that have left: vote on the outcome.
-            if (!all_epilogue_threads(mbar_wait(bar_acc_full + 8 * as, (it >> 1) & 1u, ctl, 4))) {
+            timer.start();
+            const bool acc_ready = all_epilogue_threads(mbar_wait(bar_acc_full + 8 * as, acc_phase, ctl, 4));
+            timer.stop_a();
+            if (!acc_ready) {
                 ok = false;
                 break;
             }
             ptx::tc_fence_after();
+            for (uint32_t half = 0; half < 2; ++half)
             for (uint32_t c0 = 0; c0 < ncols; c0 += 16) {
+                const uint32_t nh = nt * 2 + half;      // index of the 128-row half among the expert's rows
                 uint32_t vi[16];
-                ptx::tmem_ld16(tmem_base + lane_base + (as * mw) * bm + c0, vi);
-                if (mw == 2) {
-                    uint32_t vj[16];
-                    ptx::tmem_ld16(tmem_base + lane_base + (as * mw + 1) * bm + c0, vj);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (uint32_t c = 0; c < 16; ++c)
-                        vi[c] = __float_as_uint(__fadd_rn(__uint_as_float(vi[c]), __uint_as_float(vj[c])));
-                } else {
-                    ptx::tmem_ld_wait();
-                }
-                if (c0 + 16 >= ncols) {
+                ptx::tmem_ld16(tmem_base + lane_base + (as * 2 + half) * bm + c0, vi);
+                ptx::tmem_ld_wait();
+                if (half == 1 && c0 + 16 >= ncols) {
                     // Last read of this accumulator stage: hand it back to the MMA warps.
                     ptx::tc_fence_before();
                     __syncwarp();
@@ -421,7 +461,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     for (uint32_t c = 0; c < 16; ++c) {
                         const uint32_t col = c0 + c;
                         if (col < valid)
-                            p.raw_out[static_cast<size_t>(row0 + col) * p.w_rows + nt * kTileRows + r] =
+                            p.raw_out[static_cast<size_t>(row0 + col) * p.w_rows + nh * kHalfRows + r] =
                                 __uint_as_float(vi[c]);
                     }
                 } else if constexpr (kPhase == kPhaseL2) {
@@ -432,7 +472,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                             const uint32_t src_rank = info[col * 3], src_token = info[col * 3 + 1], slot = info[col * 3 + 2];
                             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.combine_base[src_rank]) +
                                 (static_cast<size_t>(slot) * p.capacity + src_token) * p.hidden +
-                                nt * kTileRows + r;
+                                nh * kHalfRows + r;
                             *dst = __float2bfloat16_rn(__uint_as_float(vi[c]));
                         }
                     }
@@ -441,7 +481,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     // same channels, so lane l and lane l^8 hold a channel's pair.  The
                     // gate lane finishes the even columns, the up lane the odd ones.
                     const uint32_t is_up = (r >> 3) & 1u;
-                    const uint32_t ch = nt * 64 + (r >> 4) * 8 + (r & 7u);   // intermediate channel
+                    const uint32_t ch = nh * 64 + (r >> 4) * 8 + (r & 7u);   // intermediate channel
                     float res[8], amax[8];
 #pragma unroll
                     for (uint32_t j = 0; j < 8; ++j) {
@@ -477,7 +517,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         if (col < valid) {
                             p.out_acts[static_cast<size_t>(row0 + col) * p.inter + ch] = static_cast<uint8_t>(byte);
                             if ((q & 1u) == 0u && (lane & 0x17u) == 0u) {
-                                const uint32_t k32 = nt * 2 + (q >> 1);   // index of the 32-channel group
+                                const uint32_t k32 = nh * 2 + (q >> 1);   // index of the 32-channel group
                                 const size_t word = static_cast<size_t>(k32 >> 2) * p.out_sf_stride +
                                                     static_cast<size_t>(b) * p.sf_block_m + sf_row_in_block(col);
                                 p.out_sf[word * 4 + (k32 & 3u)] = static_cast<uint8_t>(code);
@@ -488,6 +528,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 }
             }
         }
+        timer.finish(it);
     }
 
     ptx::tc_fence_before();

@@ -24,6 +24,12 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 
+__device__ __forceinline__ long long clock_cycles() {
+    long long t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t));
+    return t;
+}
+
 // True in exactly one lane of a converged warp.  Unlike `lane == 0`, the
 // compiler knows the guarded code runs in a single thread and can feed the
 // TMA / tcgen05 instructions from uniform registers directly.

@@ -133,6 +133,14 @@ int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* words);
  * descriptor and scale plumbing. */
 int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream);
 
+/* Run one of the two grouped GEMMs (which = 0 gate/up, 1 down) with per-role
+ * cycle counters written to `out`: uint64 [grid][5 roles][4] = {cycles in the
+ * role loop, cycles in its first wait, cycles in its second wait, tiles};
+ * roles: weight producer, activation producer, MMA warp 0, MMA warp 1,
+ * epilogue.  Returns the grid size.  Tuning aid; no counterpart in the
+ * reference, which has no tracing (only printf on timeouts). */
+int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
