@@ -386,3 +386,85 @@ extern "C" int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cud
     GCMOE_CUDA(cudaGetLastError());
     return GCMOE_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Layer call for callers that must not allocate device memory.
+//
+// Some hosts of this operator run with a frozen device heap: a serving loop
+// whose memory pool was sized at start-up, or a worker that is already inside
+// a region where cudaMalloc would synchronise or fail.  They cannot provide
+// the plan-private scratch block the other entry points expect.  For them the
+// scratch (status words, per-expert token counts, pool-block prefix) lives in
+// the fixed device array below, which every GPU that loads the library
+// holds until the process exits.
+// ---------------------------------------------------------------------------
+namespace gcmoe {
+
+constexpr int kStaticMaxLocalExperts = 128;
+constexpr size_t kStaticScratchBytes = 1280;   // status + counts + prefix for 128 local experts, 256-aligned
+static_assert(kStaticScratchBytes >= kStatusWords * 4 + (2 * kStaticMaxLocalExperts + 1) * 4, "static scratch too small");
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_address[kMaxDevices] = {};
+static std::mutex g_static_scratch_mutex;
+
+// Device address of g_static_scratch on the current device.  In host code the
+// array's name is only a handle; the address has to be asked for, once per
+// device, while that device is current.
+static int static_scratch_address(void** out) {
+    int device = 0;
+    GCMOE_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices)
+        return fail(GCMOE_ERR_UNSUPPORTED, "device ordinal %d is outside the static scratch table", device);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_address[device] == nullptr) {
+        void* ptr = nullptr;
+        GCMOE_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        g_static_scratch_address[device] = ptr;
+    }
+    *out = g_static_scratch_address[device];
+    return GCMOE_OK;
+}
+
+}  // namespace gcmoe
+
+extern "C" int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
+                                           void* cuda_stream) {
+    if (problem == nullptr || buffers == nullptr) return fail(GCMOE_ERR_INVALID, "null argument");
+    if (problem->num_ranks <= 0 || problem->num_experts <= 0)
+        return fail(GCMOE_ERR_INVALID, "invalid rank/expert configuration");
+    const int local = problem->num_experts / problem->num_ranks;
+    if (local > kStaticMaxLocalExperts || gcmoe_scratch_bytes(problem) > kStaticScratchBytes)
+        return fail(GCMOE_ERR_UNSUPPORTED,
+                    "%d local experts exceed the %d the built-in scratch holds; use gcmoe_plan_create "
+                    "with caller-provided scratch", local, kStaticMaxLocalExperts);
+    void* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    gcmoe_buffers with_scratch = *buffers;
+    with_scratch.scratch = reinterpret_cast<uint64_t>(scratch);
+    with_scratch.scratch_bytes = kStaticScratchBytes;
+    gcmoe_plan* plan = nullptr;
+    if (int rc = gcmoe_plan_create(problem, &with_scratch, &plan)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    // The array keeps what the previous call left: the status words must start at zero.
+    cudaError_t err = cudaMemsetAsync(scratch, 0, kStatusWords * 4, s);
+    int rc = err == cudaSuccess ? gcmoe_launch(plan, cuda_stream)
+                                : fail(GCMOE_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(err));
+    gcmoe_plan_destroy(plan);   // host object only; the enqueued kernels carry their parameters by value
+    return rc;
+}
+
+extern "C" int gcmoe_static_scratch_status(void* cuda_stream, uint32_t* words) {
+    if (words == nullptr) return fail(GCMOE_ERR_INVALID, "null argument");
+    void* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    GCMOE_CUDA(cudaMemcpyAsync(words, scratch, kStatusWords * 4, cudaMemcpyDeviceToHost, s));
+    GCMOE_CUDA(cudaStreamSynchronize(s));
+    if (words[kStatusCode] != 0)
+        return fail(GCMOE_ERR_DEVICE, "device wait gave up: code %u kernel %u site %u block %u",
+                    words[kStatusCode], words[kStatusKernel], words[kStatusSite], words[kStatusBlock]);
+    return GCMOE_OK;
+}

@@ -141,6 +141,31 @@ int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream);
  * reference, which has no tracing (only printf on timeouts). */
 int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cuda_stream);
 
+/* One layer call for callers that cannot allocate device memory (no
+ * counterpart in the reference, whose launch path allocates through its JIT
+ * and graph caches).  Meant for hosts with a frozen device heap -- a serving
+ * loop whose pool was sized at start-up, or code running where cudaMalloc
+ * would synchronise or is forbidden -- which therefore cannot hand over the
+ * scratch block gcmoe_plan_create asks for.  The kernels' scratch (status
+ * words, per-expert token counts, pool-block prefix) lives in a fixed
+ * 1280-byte device array inside the library instead, enough for 128 local
+ * experts; more local experts are rejected with GCMOE_ERR_UNSUPPORTED.
+ * `buffers->scratch` is ignored; the arena, weights and y are still the
+ * caller's.  No cudaMalloc / cudaFree or any other allocating device routine
+ * is called; one small host object lives for the duration of the call.
+ *
+ * The first call on a device looks up the array's device address; make that
+ * first call before starting any stream capture on that device.  All calls on
+ * a device share the one array: its status words are cleared on the stream
+ * before the kernels, the rest is rewritten by the dispatch kernel, and two
+ * calls whose kernels overlap on the GPU (different streams) race on it. */
+int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
+                                void* cuda_stream);
+
+/* Status words of the built-in scratch after synchronising `cuda_stream`
+ * (same meaning as gcmoe_status_read). */
+int gcmoe_static_scratch_status(void* cuda_stream, uint32_t* words);
+
 #ifdef __cplusplus
 }
 #endif
