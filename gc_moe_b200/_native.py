@@ -37,7 +37,7 @@ class Buffers(ctypes.Structure):
             'shared_sf_rows', 'y', 'stats',
             'w1', 'w1_sf', 'w2', 'w2_sf', 'w1_sf_stride', 'w2_sf_stride',
             'sw1', 'sw1_sf', 'sw2', 'sw2_sf', 'sw1_sf_stride', 'sw2_sf_stride',
-            'scratch', 'scratch_bytes')]
+            'scratch', 'scratch_bytes', 'off_exchange')]
 
 
 LIBRARY_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'libgcmoe_sm100.so')

@@ -22,12 +22,34 @@ struct CombineParams {
     const long long* topk_idx;     // [cap][k]
     __nv_bfloat16* y;              // [T][H]
     uint32_t* epoch_word;          // per-call counter in the arena (recv_parity)
+    // multi-rank: the partial rows are written by other GPUs; wait until
+    // rows x tiles contributions have landed (null on a single rank)
+    const uint32_t* call_info;     // [kCallInfoWords] written by the dispatch kernel
+    const uint32_t* combine_arrived;   // this rank's exchange::kCombineArrived
+    uint32_t* status;
+    uint64_t timeout_ns;
+    uint32_t tiles_per_row;        // H / 256: down-GEMM tiles that write one row
+    uint32_t num_ranks;
     uint32_t num_tokens, topk, hidden, capacity, num_experts, has_shared;
 };
 
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineParams p) {
     const uint32_t vecs_per_token = p.hidden / 8;
     const uint64_t total = static_cast<uint64_t>(p.num_tokens) * vecs_per_token;
+    if (p.num_ranks > 1) {
+        __shared__ uint32_t abort_word;
+        if (threadIdx.x == 0) {
+            abort_word = 0;
+            WaitCtl ctl;
+            ctl.status = p.status;
+            ctl.abort = &abort_word;
+            ctl.timeout_ns = p.timeout_ns;
+            ctl.kernel = kKernelCombine;
+            flag_wait_eq(p.combine_arrived + p.call_info[kCallGeneration] * 32,
+                         p.call_info[kCallCombineRows] * p.tiles_per_row, ctl, 1);
+        }
+        __syncthreads();
+    }
     if (blockIdx.x == 0 && threadIdx.x == 0) *p.epoch_word += 1u;   // one call retired
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kCombineThreads + threadIdx.x; i < total;
          i += static_cast<uint64_t>(gridDim.x) * kCombineThreads) {

@@ -94,6 +94,31 @@ __device__ __forceinline__ bool flag_wait_eq(const uint32_t* flag, uint32_t expe
     }
 }
 
+// Per-call words the dispatch kernel leaves in plan-private scratch for the
+// kernels that follow it in the stream.
+enum CallInfoWord : int {
+    kCallGeneration = 0,      // 0/1: which half of the double-buffered exchange this call uses
+    kCallCombineRows = 1,     // valid routes of this rank = rows its combine waits for (per H/256 tile)
+    kCallEpoch = 2,
+    kCallInfoWords = 4
+};
+
+// Cross-rank exchange block: this library's own symmetric fields.  They live
+// in the arena's `l2_full_mask` signal region (8 MiB), which the stream-ordered
+// kernels here never use for its reference purpose (ring-slot flow control).
+// Offsets are relative to the start of that region; everything is double
+// buffered by call parity ("generation").
+namespace exchange {
+constexpr uint32_t kCountsReady = 0;        // u32 [2][kMaxRanks]: epoch+1 once a source's counts landed
+constexpr uint32_t kSourceBlockM = 1024;    // u32 [2][kMaxRanks]: block-M each rank uses for its pool
+constexpr uint32_t kCombineArrived = 2048;  // u32 [2] (128 bytes apart): rows x tiles landed in combine_tokens
+constexpr uint32_t kRowsArrived = 4096;     // u32 [2][kMaxLocalExperts]: dispatched rows landed per local expert
+constexpr uint32_t kCounts = 8192;          // u32 [2][P][E]: routes of source s to global expert e
+__host__ __device__ __forceinline__ uint32_t bytes(uint32_t ranks, uint32_t experts) {
+    return kCounts + 2u * ranks * experts * 4u;
+}
+}  // namespace exchange
+
 __host__ __device__ __forceinline__ uint32_t round_up_u32(uint32_t v, uint32_t m) {
     return (v + m - 1) / m * m;
 }

@@ -1,18 +1,26 @@
 // Top-k token dispatch into the expert owners' receive pools.
 //
-// One kernel, no grid-wide barrier: every CTA recomputes the (tiny) routing
-// histogram of this rank's T x k routes, so every CTA knows each expert's
-// total and how many of an expert's routes precede the CTA's own slice of
-// routes.  A route's row in the owner's pool is then
-//     expert's first pool block x BM  +  routes of earlier source ranks
-//                                      +  rank of the route inside this source
-// which reproduces the pool order of the reference (experts ascending, source
-// ranks ascending inside an expert) with the canonical ascending token*k+slot
-// order inside one (expert, source) group, where the reference's own order is
-// whatever its atomics produced (gc_moe/impls/sm100_fp8_fp4_gc_moe.py:762-1107).
+// PUSH design, one kernel per rank, no grid-wide barrier and no pull round
+// trip.  Every CTA recomputes the (tiny) routing histogram of this rank's
+// T x k routes, so every CTA knows each expert's count and how many of an
+// expert's routes precede the CTA's own slice of routes.  With more than one
+// rank the per-expert counts are first exchanged all-to-all (each source
+// stores its E counts and its block-M into every peer's exchange block, then a
+// release flag; one NVLink hop), after which every source can compute, on its
+// own, the final pool row of each of its routes at the route's owner:
+//     expert's first pool block x BM(owner) + routes of lower source ranks
+//                                           + rank of the route inside this source
+// This is the pool order of the reference (experts ascending, source ranks
+// ascending inside an expert; gc_moe/impls/sm100_fp8_fp4_gc_moe.py:931-953)
+// with the canonical ascending token*k+slot order inside one (expert, source)
+// group, where the reference's own order is whatever its atomics produced.
 // Each warp then pushes whole rows -- FP8 payload, packed scale words, route
 // weight, source metadata, index-table entry -- straight to their final place
-// in the owner's arena; on one rank these are local stores.
+// in the owner's arena (16-byte stores over NVLink, local stores on one rank)
+// and bumps the owner's per-expert arrival counter with a system-scope release.
+// The reference instead writes indices, waits for every rank's counts and then
+// PULLS each row with a remote read (impls:997-1094): one more NVLink trip on
+// the critical path.
 //
 // Data products written (same arena regions and meaning as the reference):
 //   expert_recv_count[gen][src][l]        routes from src to local expert l
@@ -21,8 +29,8 @@
 //   token_src_metadata[pool_row]          (src_rank, src_token, slot)
 //   l1_acts[pool_row], l1_acts_sf[...], l1_topk_weights[pool_row]
 //   routed_pool_blocks                    number of pool blocks of this call
-// and, in plan-private memory, the per-expert token counts and pool-block
-// prefix the GEMM kernels schedule from.
+// and, in plan-private memory, the per-expert token counts, the pool-block
+// prefix and the call-info words the later kernels of the call read.
 #pragma once
 
 #include "device_common.cuh"
@@ -41,59 +49,123 @@ struct DispatchParams {
     uint64_t arena_base[kMaxRanks];
     uint64_t off_recv_count, off_recv_count_sum, off_routed_pool_blocks, off_recv_parity;
     uint64_t off_index_table, off_metadata, off_l1_acts, off_l1_acts_sf, off_l1_weights;
+    uint64_t off_exchange;
     // plan-private outputs
     int* expert_count;            // [E_loc]
     int* expert_block_start;      // [E_loc + 1]
+    uint32_t* call_info;          // [kCallInfoWords]
     int* stats;                   // optional cumulative per-expert counter (may be null)
     uint32_t* status;
     uint64_t timeout_ns;
     uint32_t num_ranks, rank, num_experts, local_experts;
     uint32_t num_tokens, topk, hidden, capacity;
-    uint32_t block_m, sf_block_m, sf_ring;   // sf_ring: words between K128 planes of l1_acts_sf
+    uint32_t block_m, sf_ring;    // sf_ring: words between K128 planes of l1_acts_sf
 };
 
-// Dynamic shared memory: total[E], before[E], start[E_loc + 1], then the
-// CTA's slice: expert id and destination pool row per route.
-__host__ __device__ inline uint32_t dispatch_smem_bytes(uint32_t num_experts, uint32_t local_experts,
+// Dynamic shared memory: five u32 per expert (own count, own routes before the
+// slice, total over sources, routes of lower sources, first pool block), one
+// block-M per rank, then the CTA's slice: expert id and pool row per route.
+__host__ __device__ inline uint32_t dispatch_smem_bytes(uint32_t num_experts, uint32_t num_ranks,
                                                         uint32_t slice) {
-    return (2 * num_experts + local_experts + 1 + 2 * slice) * 4;
+    return (5 * num_experts + num_ranks + 8 + 2 * slice) * 4;
 }
 
 __global__ void __launch_bounds__(kDispatchThreads)
 dispatch_kernel(const __grid_constant__ DispatchParams p) {
     extern __shared__ uint32_t smem[];
+    const uint32_t P = p.num_ranks, E = p.num_experts, EL = p.local_experts;
     const uint32_t routes = p.num_tokens * p.topk;
     const uint32_t slice = (routes + gridDim.x - 1) / gridDim.x;
     const uint32_t lo = min(blockIdx.x * slice, routes), hi = min(lo + slice, routes);
-    uint32_t* const total = smem;
-    uint32_t* const before = total + p.num_experts;
-    uint32_t* const start = before + p.num_experts;               // pool-block prefix of local experts
-    int* const slice_expert = reinterpret_cast<int*>(start + p.local_experts + 1);
+    uint32_t* const own = smem;                 // [E] routes of this rank per expert
+    uint32_t* const before = own + E;           // [E] ... of them before this CTA's slice
+    uint32_t* const total = before + E;         // [E] routes of all ranks
+    uint32_t* const lower = total + E;          // [E] routes of source ranks below this one
+    uint32_t* const first_block = lower + E;    // [E] first pool block of the expert at its owner
+    uint32_t* const bm_of = first_block + E;    // [P] block-M of each rank's pool
+    uint32_t* const misc = bm_of + P;           // [8] abort word, own pool blocks, own valid routes
+    int* const slice_expert = reinterpret_cast<int*>(misc + 8);
     uint32_t* const slice_row = reinterpret_cast<uint32_t*>(slice_expert + slice);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    for (uint32_t i = tid; i < 2 * p.num_experts; i += kDispatchThreads) total[i] = 0;
+    uint8_t* const my_arena = reinterpret_cast<uint8_t*>(p.arena_base[p.rank]);
+    // Calls alternate between the two halves of every double-buffered counter;
+    // the combine kernel bumps the call counter when a call retires, so replays
+    // of a captured graph alternate without host involvement.
+    const uint32_t epoch = *reinterpret_cast<const uint32_t*>(my_arena + p.off_recv_parity);
+    const uint32_t gen = epoch & 1u;
+
+    WaitCtl ctl;
+    ctl.status = p.status;
+    ctl.abort = misc;
+    ctl.timeout_ns = p.timeout_ns;
+    ctl.kernel = kKernelDispatch;
+
+    for (uint32_t i = tid; i < 2 * E; i += kDispatchThreads) own[i] = 0;
+    if (tid < 8) misc[tid] = 0;
     __syncthreads();
     // A route is valid iff its expert id, compared as unsigned 64-bit, is below
     // the expert count (negative ids mean "no route").
     for (uint32_t a = tid; a < routes; a += kDispatchThreads) {
         const unsigned long long e = static_cast<unsigned long long>(p.topk_idx[a]);
-        if (e < p.num_experts) {
-            atomicAdd(&total[e], 1u);
+        if (e < E) {
+            atomicAdd(&own[e], 1u);
             if (a < lo) atomicAdd(&before[e], 1u);
         }
     }
     __syncthreads();
 
-    // Pool-block prefix over this rank's local experts (single rank: every
-    // route of a local expert comes from this rank).
-    const uint32_t first_local = p.rank * p.local_experts;
-    if (warp == 0) {
-        const uint32_t per_lane = (p.local_experts + 31) / 32;
+    if (P > 1) {
+        // ---- all-to-all of the counts: CTA c serves peers c, c + grid, ...
+        for (uint32_t peer = blockIdx.x; peer < P; peer += gridDim.x) {
+            uint8_t* const ex = reinterpret_cast<uint8_t*>(p.arena_base[peer]) + p.off_exchange;
+            uint32_t* const counts = reinterpret_cast<uint32_t*>(ex + exchange::kCounts) +
+                                     (static_cast<size_t>(gen) * P + p.rank) * E;
+            for (uint32_t e = tid; e < E; e += kDispatchThreads) counts[e] = own[e];
+            if (tid == 0)
+                reinterpret_cast<uint32_t*>(ex + exchange::kSourceBlockM)[gen * kMaxRanks + p.rank] = p.block_m;
+            __syncthreads();
+            if (tid == 0) {
+                ptx::fence_acq_rel_sys();
+                ptx::st_release_sys(reinterpret_cast<uint32_t*>(ex + exchange::kCountsReady) + gen * kMaxRanks + p.rank,
+                                    epoch + 1u);
+            }
+        }
+        // ---- wait for every source's counts (one lane per source, bounded)
+        const uint8_t* const ex = my_arena + p.off_exchange;
+        for (uint32_t s = tid; s < P; s += kDispatchThreads)
+            flag_wait_eq(reinterpret_cast<const uint32_t*>(ex + exchange::kCountsReady) + gen * kMaxRanks + s,
+                         epoch + 1u, ctl, 1);
+        __syncthreads();
+        if (*ctl.abort) return;        // the whole CTA leaves together; the host reads the status block
+        const uint32_t* const counts = reinterpret_cast<const uint32_t*>(ex + exchange::kCounts) +
+                                       static_cast<size_t>(gen) * P * E;
+        for (uint32_t e = tid; e < E; e += kDispatchThreads) {
+            uint32_t n = 0, below = 0;
+            for (uint32_t s = 0; s < P; ++s) {
+                const uint32_t c = counts[static_cast<size_t>(s) * E + e];
+                if (s < p.rank) below += c;
+                n += c;
+            }
+            total[e] = n;
+            lower[e] = below;
+        }
+        for (uint32_t s = tid; s < P; s += kDispatchThreads)
+            bm_of[s] = reinterpret_cast<const uint32_t*>(ex + exchange::kSourceBlockM)[gen * kMaxRanks + s];
+    } else {
+        for (uint32_t e = tid; e < E; e += kDispatchThreads) { total[e] = own[e]; lower[e] = 0; }
+        if (tid == 0) bm_of[0] = p.block_m;
+    }
+    __syncthreads();
+
+    // Pool-block prefix of every owner's local experts (warp w: owners w, w+8, ...).
+    for (uint32_t r = warp; r < P; r += kDispatchThreads / 32) {
+        const uint32_t bm = bm_of[r], base = r * EL;
+        const uint32_t per_lane = (EL + 31) / 32;
         uint32_t sum = 0;
         for (uint32_t i = 0; i < per_lane; ++i) {
             const uint32_t l = lane * per_lane + i;
-            if (l < p.local_experts) sum += (total[first_local + l] + p.block_m - 1) / p.block_m;
+            if (l < EL) sum += (total[base + l] + bm - 1) / bm;
         }
         uint32_t incl = sum;
         for (uint32_t d = 1; d < 32; d <<= 1) {
@@ -103,59 +175,78 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         uint32_t run = incl - sum;
         for (uint32_t i = 0; i < per_lane; ++i) {
             const uint32_t l = lane * per_lane + i;
-            if (l < p.local_experts) {
-                start[l] = run;
-                run += (total[first_local + l] + p.block_m - 1) / p.block_m;
+            if (l < EL) {
+                first_block[base + l] = run;
+                run += (total[base + l] + bm - 1) / bm;
             }
         }
-        if (lane == 31) start[p.local_experts] = incl;
+        if (r == p.rank && lane == 31) misc[1] = incl;      // pool blocks of this rank
+    }
+    if (blockIdx.x == 0) {
+        uint32_t mine = 0;
+        for (uint32_t e = tid; e < E; e += kDispatchThreads) mine += own[e];
+        for (uint32_t d = 16; d > 0; d >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, d);
+        if (lane == 0) atomicAdd(&misc[2], mine);            // valid routes of this rank
     }
     __syncthreads();
 
-    uint8_t* const my_arena = reinterpret_cast<uint8_t*>(p.arena_base[p.rank]);
-    // The receive counters are double-buffered by call parity; the combine
-    // kernel bumps the call counter when a call retires, so replays of a
-    // captured graph alternate without host involvement.
-    const uint32_t generation = *reinterpret_cast<const uint32_t*>(my_arena + p.off_recv_parity) & 1u;
+    const uint32_t first_local = p.rank * EL;
     if (blockIdx.x == 0) {
+        // ---- what this rank receives: the reference's count products and the
+        // tables the GEMM kernels schedule from
         unsigned long long* recv = reinterpret_cast<unsigned long long*>(my_arena + p.off_recv_count) +
-            static_cast<size_t>(generation) * p.num_ranks * p.local_experts +
-            static_cast<size_t>(p.rank) * p.local_experts;
+            static_cast<size_t>(gen) * P * EL;
         unsigned long long* recv_sum = reinterpret_cast<unsigned long long*>(my_arena + p.off_recv_count_sum) +
-            static_cast<size_t>(generation) * p.local_experts;
-        for (uint32_t l = tid; l < p.local_experts; l += kDispatchThreads) {
+            static_cast<size_t>(gen) * EL;
+        const uint32_t* const counts = reinterpret_cast<const uint32_t*>(my_arena + p.off_exchange + exchange::kCounts) +
+            static_cast<size_t>(gen) * P * E;
+        for (uint32_t l = tid; l < EL; l += kDispatchThreads) {
             const uint32_t n = total[first_local + l];
             p.expert_count[l] = static_cast<int>(n);
-            p.expert_block_start[l] = static_cast<int>(start[l]);
-            recv[l] = n;
+            p.expert_block_start[l] = static_cast<int>(first_block[first_local + l]);
+            for (uint32_t s = 0; s < P; ++s)
+                recv[static_cast<size_t>(s) * EL + l] = P > 1 ? counts[static_cast<size_t>(s) * E + first_local + l] : n;
             // high word: number of source ranks that have reported
-            recv_sum[l] = (static_cast<unsigned long long>(p.num_ranks) << 32) | n;
+            recv_sum[l] = (static_cast<unsigned long long>(P) << 32) | n;
             if (p.stats != nullptr) p.stats[l] += static_cast<int>(n);
         }
+        if (P > 1) {
+            // Counters of the NEXT call's generation start from zero; nobody can be
+            // adding to them yet (a peer reaches its next call only after this
+            // rank has finished the current one).
+            uint8_t* const ex = my_arena + p.off_exchange;
+            uint32_t* const arrived_next = reinterpret_cast<uint32_t*>(ex + exchange::kRowsArrived) + (gen ^ 1u) * kMaxLocalExperts;
+            for (uint32_t l = tid; l < EL; l += kDispatchThreads) arrived_next[l] = 0;
+            if (tid == 0) *reinterpret_cast<uint32_t*>(ex + exchange::kCombineArrived + (gen ^ 1u) * 128) = 0;
+        }
         if (tid == 0) {
-            p.expert_block_start[p.local_experts] = static_cast<int>(start[p.local_experts]);
-            *reinterpret_cast<uint32_t*>(my_arena + p.off_routed_pool_blocks) = start[p.local_experts];
+            p.expert_block_start[EL] = static_cast<int>(misc[1]);
+            *reinterpret_cast<uint32_t*>(my_arena + p.off_routed_pool_blocks) = misc[1];
+            p.call_info[kCallGeneration] = gen;
+            p.call_info[kCallCombineRows] = misc[2];
+            p.call_info[kCallEpoch] = epoch;
         }
     }
 
     // Destination of every route in this CTA's slice.
     for (uint32_t a = lo + tid; a < hi; a += kDispatchThreads) {
         const unsigned long long e64 = static_cast<unsigned long long>(p.topk_idx[a]);
-        slice_expert[a - lo] = e64 < p.num_experts ? static_cast<int>(e64) : -1;
+        slice_expert[a - lo] = e64 < E ? static_cast<int>(e64) : -1;
     }
     __syncthreads();
     for (uint32_t a = lo + tid; a < hi; a += kDispatchThreads) {
         const int e = slice_expert[a - lo];
         uint32_t row = 0xFFFFFFFFu;
         if (e >= 0) {
-            uint32_t i = before[e];
+            uint32_t i = before[e];                       // position among this source's routes to e
             for (uint32_t j = 0; j < a - lo; ++j) i += (slice_expert[j] == e);
-            const uint32_t owner = static_cast<uint32_t>(e) / p.local_experts;
-            const uint32_t l = static_cast<uint32_t>(e) - owner * p.local_experts;
-            row = start[l] * p.block_m + i;
+            const uint32_t owner = static_cast<uint32_t>(e) / EL;
+            const uint32_t l = static_cast<uint32_t>(e) - owner * EL;
+            row = first_block[e] * bm_of[owner] + lower[e] + i;
             uint8_t* const dst_arena = reinterpret_cast<uint8_t*>(p.arena_base[owner]);
-            reinterpret_cast<uint32_t*>(dst_arena + p.off_index_table)[
-                (static_cast<size_t>(l) * p.num_ranks + p.rank) * p.capacity + i] = a;
+            if (i < p.capacity)
+                reinterpret_cast<uint32_t*>(dst_arena + p.off_index_table)[
+                    (static_cast<size_t>(l) * P + p.rank) * p.capacity + i] = a;
             uint32_t* meta = reinterpret_cast<uint32_t*>(dst_arena + p.off_metadata) + static_cast<size_t>(row) * 3;
             meta[0] = p.rank;
             meta[1] = a / p.topk;
@@ -166,23 +257,35 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     }
     __syncthreads();
 
-    // One warp per route: copy the FP8 row (16 bytes per lane per step) and
-    // scatter its packed scale words into the MN-major scale ring.
+    // One warp per route: copy the FP8 row (16 bytes per lane per step), scatter
+    // its packed scale words into the owner's MN-major scale ring, then tell the
+    // owner one more row of that expert has landed.
     const uint32_t row_vecs = p.hidden / 16, sf_words = p.hidden / 128;
     for (uint32_t a = lo + warp; a < hi; a += kDispatchThreads / 32) {
         const uint32_t row = slice_row[a - lo];
         if (row == 0xFFFFFFFFu) continue;
-        const uint32_t owner = static_cast<uint32_t>(slice_expert[a - lo]) / p.local_experts;
+        const uint32_t e = static_cast<uint32_t>(slice_expert[a - lo]);
+        const uint32_t owner = e / EL;
+        const uint32_t bm = bm_of[owner], sf_block = round_up_u32(bm, 128);
         uint8_t* const dst_arena = reinterpret_cast<uint8_t*>(p.arena_base[owner]);
         const uint32_t t = a / p.topk;
         const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(t) * p.hidden);
         uint4* dst = reinterpret_cast<uint4*>(dst_arena + p.off_l1_acts + static_cast<size_t>(row) * p.hidden);
+#pragma unroll 4
         for (uint32_t v = lane; v < row_vecs; v += 32) dst[v] = src[v];
-        const uint32_t block = row / p.block_m, u = row - block * p.block_m;
-        const uint32_t sf_row = block * p.sf_block_m + sf_row_in_block(u);
+        const uint32_t block = row / bm, u = row - block * bm;
+        const uint32_t sf_row = block * sf_block + sf_row_in_block(u);
         uint32_t* sf_dst = reinterpret_cast<uint32_t*>(dst_arena + p.off_l1_acts_sf);
         for (uint32_t w = lane; w < sf_words; w += 32)
             sf_dst[static_cast<size_t>(w) * p.sf_ring + sf_row] = p.x_sf[static_cast<size_t>(t) * sf_words + w];
+        if (P > 1) {
+            __syncwarp();
+            if (lane == 0) {
+                ptx::fence_acq_rel_sys();
+                ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(dst_arena + p.off_exchange + exchange::kRowsArrived) +
+                                             gen * kMaxLocalExperts + (e - owner * EL), 1u);
+            }
+        }
     }
 }
 

@@ -121,8 +121,6 @@ static int check_problem(const gcmoe_problem& q) {
     const long long routes = 1ll * q.num_ranks * q.capacity * (q.topk < local ? q.topk : local);
     if (q.ring_tokens < routes + local * (bm - 1))
         return fail(GCMOE_ERR_UNSUPPORTED, "ring of %d rows cannot hold the whole receive pool", q.ring_tokens);
-    if (q.num_ranks > 1)
-        return fail(GCMOE_ERR_UNSUPPORTED, "multi-rank dispatch is not built into this library version");
     if (q.num_shared_experts != 0)
         return fail(GCMOE_ERR_UNSUPPORTED, "the fused shared expert is not built into this library version");
     return GCMOE_OK;
@@ -135,7 +133,7 @@ extern "C" const char* gcmoe_last_error(void) { return g_error; }
 extern "C" size_t gcmoe_scratch_bytes(const gcmoe_problem* problem) {
     if (problem == nullptr || problem->num_ranks <= 0) return 0;
     const size_t local = size_t(problem->num_experts / problem->num_ranks);
-    return round_up_u32(uint32_t(kStatusWords * 4 + (2 * local + 1) * 4), 256);
+    return round_up_u32(uint32_t(kStatusWords * 4 + (2 * local + 1) * 4 + kCallInfoWords * 4), 256);
 }
 
 extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
@@ -158,6 +156,15 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         return fail(GCMOE_ERR_INVALID, "weight scales must be MN-major with a 4-aligned K stride");
     if (b.scratch == 0 || b.scratch % 16 || b.scratch_bytes < gcmoe_scratch_bytes(problem))
         return fail(GCMOE_ERR_INVALID, "scratch block missing or too small");
+    if (q.num_ranks > 1) {
+        for (int r = 0; r < q.num_ranks; ++r)
+            if (b.arena_base[r] == 0 || b.arena_base[r] % 16)
+                return fail(GCMOE_ERR_INVALID, "arena of rank %d is not mapped", r);
+        if (b.off_exchange == 0 || b.off_exchange % 128 ||
+            exchange::bytes(q.num_ranks, q.num_experts) > (8u << 20))
+            return fail(GCMOE_ERR_INVALID, "exchange block missing or too small for %d ranks x %d experts",
+                        q.num_ranks, q.num_experts);
+    }
 
     GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kPhaseL1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kPhaseL2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
@@ -188,6 +195,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     plan->status = reinterpret_cast<uint32_t*>(b.scratch);
     int* expert_count = reinterpret_cast<int*>(b.scratch + kStatusWords * 4);
     int* expert_block_start = expert_count + EL;
+    uint32_t* call_info = reinterpret_cast<uint32_t*>(expert_block_start + EL + 1);
 
     // ---- dispatch
     DispatchParams& d = plan->dispatch;
@@ -206,6 +214,8 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     d.off_l1_acts = b.off_l1_acts;
     d.off_l1_acts_sf = b.off_l1_acts_sf;
     d.off_l1_weights = b.off_l1_topk_weights;
+    d.off_exchange = b.off_exchange;
+    d.call_info = call_info;
     d.expert_count = expert_count;
     d.expert_block_start = expert_block_start;
     d.stats = reinterpret_cast<int*>(b.stats);
@@ -213,13 +223,13 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     d.timeout_ns = timeout_ns;
     d.num_ranks = P; d.rank = q.rank; d.num_experts = E; d.local_experts = EL;
     d.num_tokens = q.num_tokens; d.topk = q.topk; d.hidden = H; d.capacity = q.capacity;
-    d.block_m = bm; d.sf_block_m = sfbm; d.sf_ring = q.sf_ring_tokens;
+    d.block_m = bm; d.sf_ring = q.sf_ring_tokens;
     const uint32_t routes = uint32_t(q.num_tokens) * q.topk;
     const uint32_t warps = kDispatchThreads / 32;
     uint32_t dgrid = (routes + warps - 1) / warps;
     dgrid = dgrid < 1 ? 1 : (dgrid > uint32_t(plan->num_sms) ? plan->num_sms : dgrid);
     plan->dispatch_grid = dgrid;
-    plan->dispatch_smem = dispatch_smem_bytes(E, EL, (routes + dgrid - 1) / dgrid);
+    plan->dispatch_smem = dispatch_smem_bytes(E, P, (routes + dgrid - 1) / dgrid);
     if (plan->dispatch_smem > uint32_t(kSmemLimit))
         return bail(fail(GCMOE_ERR_UNSUPPORTED, "dispatch slice does not fit shared memory"));
 
@@ -253,6 +263,11 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.capacity = q.capacity;
         g.hidden = H;
         g.inter = I;
+        g.num_ranks = P;
+        g.call_info = call_info;
+        g.rows_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kRowsArrived);
+        for (uint32_t r = 0; r < P; ++r)
+            g.combine_arrived[r] = b.arena_base[r] + b.off_exchange + exchange::kCombineArrived;
     };
     auto encode_pair = [&](GemmParams& g, uint64_t acts, uint32_t k, uint64_t weights, uint32_t w_rows,
                            const char* what) -> int {
@@ -298,7 +313,8 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     uint64_t max_blocks = (all_routes < EL ? all_routes : EL) + all_routes / bm;
     if (max_blocks < 1) max_blocks = 1;
     auto grid_for = [&](uint32_t n_tiles) {
-        const uint64_t tiles = max_blocks * n_tiles;
+        // With several ranks the pool depends on what the other ranks send.
+        const uint64_t tiles = P > 1 ? uint64_t(plan->num_sms) : max_blocks * n_tiles;
         return uint32_t(tiles < uint64_t(plan->num_sms) ? tiles : uint64_t(plan->num_sms));
     };
     plan->gemm_grid_l1 = grid_for(g1.n_tiles);
@@ -313,6 +329,12 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     c.epoch_word = reinterpret_cast<uint32_t*>(arena + b.off_recv_parity);
     c.num_tokens = q.num_tokens; c.topk = q.topk; c.hidden = H; c.capacity = q.capacity;
     c.num_experts = E; c.has_shared = 0;
+    c.num_ranks = P;
+    c.call_info = call_info;
+    c.combine_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kCombineArrived);
+    c.status = plan->status;
+    c.timeout_ns = timeout_ns;
+    c.tiles_per_row = H / kTileRows;
     const uint64_t cvecs = uint64_t(q.num_tokens) * (H / 8);
     uint64_t cgrid = (cvecs + kCombineThreads - 1) / kCombineThreads;
     const uint64_t cmax = uint64_t(plan->num_sms) * 8;
@@ -402,7 +424,7 @@ namespace gcmoe {
 
 constexpr int kStaticMaxLocalExperts = 128;
 constexpr size_t kStaticScratchBytes = 1280;   // status + counts + prefix for 128 local experts, 256-aligned
-static_assert(kStaticScratchBytes >= kStatusWords * 4 + (2 * kStaticMaxLocalExperts + 1) * 4, "static scratch too small");
+static_assert(kStaticScratchBytes >= kStatusWords * 4 + (2 * kStaticMaxLocalExperts + 1) * 4 + kCallInfoWords * 4, "static scratch too small");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 

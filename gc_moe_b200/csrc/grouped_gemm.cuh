@@ -94,6 +94,12 @@ struct GemmParams {
     uint32_t hidden;
     // ---- raw epilogue (kPhaseRaw): FP32 accumulators, [rows][w_rows]
     float* raw_out;
+    // ---- multi-rank: arrival counters of the dispatched rows (gate/up) and of
+    // the combine contributions (down); null / 1 on a single rank
+    const uint32_t* call_info;        // [kCallInfoWords] written by the dispatch kernel
+    const uint32_t* rows_arrived;     // this rank's exchange::kRowsArrived, [2][kMaxLocalExperts]
+    uint64_t combine_arrived[kMaxRanks];  // address of exchange::kCombineArrived on each rank
+    uint32_t num_ranks;
     // ---- optional role timing: [grid][kTimingRoles][kTimingWords] clock64 totals, or null
     unsigned long long* timing;
 };
@@ -292,7 +298,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const bool weights = warp == 0;
         const uint32_t tx = weights ? p.weight_tx_bytes + kWeightSfStageBytes : bm * kTileK + p.sf_block_m * 4;
         StageCursor cur;
-        uint32_t armed = 0, armed_parity = 0, ntiles = 0;
+        uint32_t armed = 0, armed_parity = 0, ntiles = 0, ready_expert = 0xFFFFFFFFu;
         bool ok = true;
         RoleTimer timer(p.timing, weights ? 0 : 1);
         for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++ntiles) {
@@ -300,6 +306,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t e = expert_of_block(b);
             const uint32_t* wsf = p.w_sf + static_cast<size_t>(e) * p.k_blocks * p.w_sf_stride + nt * kTileRows;
             const uint32_t* asf = p.act_sf + static_cast<size_t>(b) * p.sf_block_m;
+            if (kPhase != kPhaseL2 && !weights && p.num_ranks > 1 && e != ready_expert) {
+                // The rows of this expert are pushed by other GPUs: wait until all of
+                // them have landed, then order the TMA (async proxy) after the acquire.
+                uint32_t landed = 1;
+                if (lane == 0)
+                    landed = flag_wait_eq(p.rows_arrived + p.call_info[kCallGeneration] * kMaxLocalExperts + e,
+                                          static_cast<uint32_t>(tbl_count[e]), ctl, 5);
+                if (!__shfl_sync(0xffffffffu, landed, 0)) { ok = false; break; }
+                ptx::fence_proxy_async_global();
+                ready_expert = e;
+            }
             for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
                 timer.start();
                 const bool got = mbar_wait(bar_empty + 8 * cur.stage, cur.phase ^ 1u, ctl, 1);
@@ -427,6 +444,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // Stage what the stores need to know about the block's rows while the
             // main loop is still running: route weight (gate/up) or destination.
             uint32_t* const info = row_info + (it & 1u) * bm * 4;
+            if (kPhase == kPhaseL1 && p.num_ranks > 1) {
+                // Route weights are pushed by other GPUs together with the rows.
+                bool landed = true;
+                if (etid == 0)
+                    landed = flag_wait_eq(p.rows_arrived + p.call_info[kCallGeneration] * kMaxLocalExperts + e,
+                                          static_cast<uint32_t>(tbl_count[e]), ctl, 6);
+                if (!all_epilogue_threads(landed)) { ok = false; break; }
+            }
             if constexpr (kPhase == kPhaseL1) {
                 for (uint32_t i = etid; i < valid; i += 128)
                     info[i] = __float_as_uint(p.route_weight[row0 + i]);
@@ -525,6 +550,26 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         }
                     }
                     xbuf ^= 1u;
+                }
+            }
+            if (kPhase == kPhaseL2 && p.num_ranks > 1) {
+                // Tell each source rank how many of its rows this tile has written
+                // (rows of one source are contiguous in a block).  The barrier orders
+                // every epilogue thread's stores before the leader's release.
+                epilogue_barrier();
+                if (etid == 0) {
+                    ptx::fence_acq_rel_sys();
+                    const uint32_t gen = p.call_info[kCallGeneration];
+                    uint32_t run_rank = info[0], run = 0;
+                    for (uint32_t i = 0; i <= valid; ++i) {
+                        const uint32_t rk = i < valid ? info[i * 3] : 0xFFFFFFFFu;
+                        if (rk != run_rank) {
+                            ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(p.combine_arrived[run_rank] + gen * 128), run);
+                            run_rank = rk;
+                            run = 0;
+                        }
+                        ++run;
+                    }
                 }
             }
         }

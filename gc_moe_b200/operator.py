@@ -95,6 +95,7 @@ def _build_plan(config: ValidatedCall, y, l1_weights, l2_weights, call_buffer,
         buf.sw2, buf.sw2_sf = shared_l2[0].data_ptr(), shared_l2[1].data_ptr()
         buf.sw1_sf_stride, buf.sw2_sf_stride = shared_l1[1].stride(-1), shared_l2[1].stride(-1)
     buf.scratch, buf.scratch_bytes = scratch.data_ptr(), scratch.numel()
+    buf.off_exchange = SIGNAL_OFFSETS['l2_full_mask']
     handle = ctypes.c_void_p()
     _native.raise_for(lib.gcmoe_plan_create(ctypes.byref(prob), ctypes.byref(buf),
                                             ctypes.byref(handle)))

@@ -84,6 +84,10 @@ typedef struct gcmoe_buffers {
     uint64_t sw1_sf_stride, sw2_sf_stride;
     uint64_t scratch;             /* gcmoe_scratch_bytes() bytes, zero-filled    */
     uint64_t scratch_bytes;
+    uint64_t off_exchange;        /* multi-rank only: byte offset of 8 MiB of the
+                                   * arena for this library's own cross-rank
+                                   * counters; the reference layout's unused
+                                   * `l2_full_mask` signal region                */
 } gcmoe_buffers;
 
 typedef struct gcmoe_plan gcmoe_plan;
@@ -95,7 +99,7 @@ int gcmoe_version(void);
 const char* gcmoe_last_error(void);
 
 /* Bytes of plan-private device scratch a plan for `problem` needs (status
- * block, per-expert counts, pool-block prefix).  The caller allocates and
+ * block, per-expert counts, pool-block prefix, call info).  The caller allocates and
  * zero-fills it once. */
 size_t gcmoe_scratch_bytes(const gcmoe_problem* problem);
 

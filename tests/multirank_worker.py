@@ -1,0 +1,162 @@
+"""Worker of the multi-GPU parity test: one process per GPU (torchrun), NCCL
+for rendezvous only.  Every rank regenerates all ranks' seeded inputs, runs the
+collective layer call on its own tokens, and compares what it holds afterwards
+-- dispatch data products of its local experts and its y -- with the CPU oracle
+of the whole world.  Prints one JSON line per rank; exit code 0 iff all pass."""
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+import gc_moe_b200 as G
+from gc_moe_b200 import quant
+from gc_moe_b200.layout import round_up, sf_row_in_block
+from oracle import gcmoe_oracle as O
+
+COSINE_MIN, MAX_REL_ERR = 0.9999, 2.0 ** -6
+
+
+def main():
+    rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
+    torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', rank)))
+    dev = torch.device('cuda', torch.cuda.current_device())
+    os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+    dist.init_process_group('nccl', device_id=dev)
+    group = dist.group.WORLD
+    E, H, I, K, CAP = 8 * world, 1024, 512, 4, 1920
+    EL = E // world
+
+    g = torch.Generator(device=dev).manual_seed(5)
+    packs = []
+    for rows, k in ((2 * I, H), (H, I)):
+        w = torch.randn((E, rows, k), device=dev, generator=g) * 0.02
+        packs.append(quant.quantize_weights_fp4(w))
+    (q1, c1), (q2, c2) = packs
+    mine = slice(rank * EL, (rank + 1) * EL)
+    l1, l2 = G.transform_weights_for_gc_moe(
+        (q1[mine].contiguous(), quant.weight_scales_mn_major(c1[mine].contiguous())),
+        (q2[mine].contiguous(), quant.weight_scales_mn_major(c2[mine].contiguous())))
+    cpu_w = [t.cpu() for t in (q1, c1, q2, c2)]
+    buf = G.get_symm_buffer_for_gc_moe(group, E, CAP, K, H, I)
+    stats = torch.zeros(EL, dtype=torch.int32, device=dev)
+    failures, report = [], {}
+
+    def inputs_of(case, r):
+        tokens = case['tokens'][r]
+        xq, xsf, idx, w = O.make_tokens(tokens, H, E, K, seed=case['seed'] * 100 + r)
+        if case.get('invalid') and tokens:
+            idx[::3, 0] = -1
+            idx[1::4, 1] = E + 2
+        if case.get('hot') is not None and tokens:
+            idx[:, 0] = case['hot']
+            idx[:, 1] = (case['hot'] + 1) % E
+        return xq, xsf, idx, w
+
+    def stage(inp):
+        xq, xsf, idx, w = inp
+        t = xq.shape[0]
+        buf.x[:t].copy_(xq.to(dev)); buf.x_sf[:t].copy_(xsf.to(dev))
+        buf.topk_idx[:t].copy_(idx.to(dev)); buf.topk_weights[:t].copy_(w.to(dev))
+
+    def check(name, cond):
+        if not cond:
+            failures.append(name)
+
+    cases = [
+        {'name': 'uniform', 'tokens': [24] * world, 'seed': 1},
+        {'name': 'asymmetric', 'tokens': [(37 * (r + 1)) % 90 for r in range(world)], 'seed': 2},
+        {'name': 'one_idle', 'tokens': [0 if r == 0 else 16 for r in range(world)], 'seed': 3},
+        {'name': 'invalid_routes', 'tokens': [20] * world, 'seed': 4, 'invalid': True},
+        {'name': 'hot_expert', 'tokens': [150] * world, 'seed': 5, 'hot': 1},
+        {'name': 'single_token', 'tokens': [1] * world, 'seed': 6},
+    ]
+    expected_stats = np.zeros(EL, np.int64)
+    for case in cases:
+        all_inputs = [inputs_of(case, r) for r in range(world)]
+        bms = [G.get_block_m_for_gc_moe(world, E, CAP, case['tokens'][r], K) for r in range(world)]
+        ref = O.moe_layer([a[0] for a in all_inputs], [a[1] for a in all_inputs],
+                          [a[2] for a in all_inputs], [a[3] for a in all_inputs], *cpu_w, bms, clamp=10.0)
+        t = case['tokens'][rank]
+        stage(all_inputs[rank])
+        y = torch.full((t, H), float('nan'), dtype=torch.bfloat16, device=dev)
+        gen = int(buf.region('recv_parity').view(torch.int32)[0].item()) & 1
+        dist.barrier()
+        G.fp8_fp4_gc_moe(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=10.0)
+        torch.cuda.synchronize()
+        try:
+            buf.raise_on_device_error()
+        except RuntimeError as exc:
+            failures.append(f"{case['name']}: {exc}")
+            break
+        dist.barrier()
+        d, bm = ref.dispatch[rank], bms[rank]
+        expected_stats += d.counts.sum(0)
+        counts = buf.region('expert_recv_count').view(torch.int64)[gen * world * EL:(gen + 1) * world * EL]
+        check(case['name'] + ':counts', np.array_equal(counts.cpu().numpy().reshape(world, EL), d.counts))
+        check(case['name'] + ':pool_blocks', int(buf.region('routed_pool_blocks').view(torch.int32)[0]) == d.pool_blocks)
+        rows = d.pool_blocks * bm
+        valid = np.nonzero(d.metadata[:, 0] >= 0)[0]
+        meta = buf.region('token_src_metadata').view(torch.int32).reshape(-1, 3)[:rows].cpu().numpy()
+        check(case['name'] + ':metadata', np.array_equal(meta[valid], d.metadata[valid]))
+        acts = buf.l1_acts.view(torch.uint8)[:rows].cpu().numpy()
+        check(case['name'] + ':rows', np.array_equal(acts[valid], d.rows[valid]))
+        wts = buf.buffer.narrow(0, buf.layout.views['l1_topk_weights'].offset, rows * 4).view(torch.float32).cpu().numpy()
+        check(case['name'] + ':weights', np.array_equal(wts[valid], d.weights[valid]))
+        sf = buf.l1_acts_sf[:d.pool_blocks * round_up(bm, 128)].cpu().numpy()
+        sf_rows = np.array([(r // bm) * round_up(bm, 128) + sf_row_in_block(r % bm) for r in valid], dtype=np.int64)
+        check(case['name'] + ':scales', np.array_equal(sf[sf_rows], d.sf_words[valid]) if len(valid) else True)
+        table = buf.region('src_token_topk_idx').view(torch.int32).reshape(E, CAP)[:EL * world].cpu().numpy().reshape(EL, world, CAP)
+        check(case['name'] + ':index_table', all(np.array_equal(table[l, s, :len(v)].astype(np.uint32), v)
+                                                 for (l, s), v in d.index_lists.items()))
+        yc = y.cpu()
+        if t:
+            cos, err = O.cosine(yc, ref.y[rank]), O.max_rel_err(yc, ref.y[rank])
+            report[case['name']] = [round(cos, 9), err]
+            check(case['name'] + ':y', bool(torch.isfinite(yc.float()).all()) and cos >= COSINE_MIN and err <= MAX_REL_ERR)
+    check('stats', np.array_equal(stats.cpu().numpy(), expected_stats))
+
+    # Graph capture + alternating replays at fixed addresses.
+    if not failures:
+        a = {'tokens': [12] * world, 'seed': 21}
+        b = {'tokens': [12] * world, 'seed': 22}
+        y = torch.empty((12, H), dtype=torch.bfloat16, device=dev)
+        eager = []
+        for case in (a, b):
+            stage(inputs_of(case, rank)); dist.barrier()
+            G.fp8_fp4_gc_moe(y, l1, l2, buf, activation_clamp=10.0)
+            torch.cuda.synchronize(); dist.barrier()
+            eager.append(y.cpu().clone())
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                G.fp8_fp4_gc_moe(y, l1, l2, buf, activation_clamp=10.0)
+        torch.cuda.current_stream().wait_stream(side)
+        for it in range(10):
+            stage(inputs_of((a, b)[it & 1], rank))
+            y.fill_(float('nan'))
+            torch.cuda.synchronize(); dist.barrier()
+            graph.replay()
+            torch.cuda.synchronize()
+            check(f'replay{it}', torch.equal(y.cpu().view(torch.int16), eager[it & 1].view(torch.int16)))
+        try:
+            buf.raise_on_device_error()
+        except RuntimeError as exc:
+            failures.append(f'replay: {exc}')
+        dist.barrier()
+    print(json.dumps({'rank': rank, 'world': world, 'failures': failures, 'y': report}), flush=True)
+    buf.destroy()
+    dist.destroy_process_group()
+    sys.exit(1 if failures else 0)
+
+
+if __name__ == '__main__':
+    main()

@@ -51,6 +51,7 @@ def describe_call(case, y, clamp, fast_math):
                         ('off_l2_acts', 'l2_acts'), ('off_l2_acts_sf', 'l2_acts_sf'),
                         ('off_combine_tokens', 'combine_tokens')):
         setattr(buf, field, lay.views[view].offset)
+    buf.off_exchange = SIGNAL_OFFSETS['l2_full_mask']
     buf.y = y.data_ptr()
     buf.w1, buf.w1_sf = case.l1[0].data_ptr(), case.l1[1].data_ptr()
     buf.w2, buf.w2_sf = case.l2[0].data_ptr(), case.l2[1].data_ptr()
