@@ -19,7 +19,12 @@ def _run(world):
     cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={world}',
            '--master-addr', '127.0.0.1', '--master-port', str(29650 + world), WORKER]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
-    lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith('{"rank"')]
+    # ranks share stdout: two JSON objects may end up on one line
+    lines, decoder, text, pos = [], json.JSONDecoder(), out.stdout, 0
+    while (pos := text.find('{"rank"', pos)) >= 0:
+        obj, end = decoder.raw_decode(text, pos)
+        lines.append(obj)
+        pos = end
     assert len(lines) == world, out.stdout[-2000:] + out.stderr[-4000:]
     for line in lines:
         assert line['failures'] == [], line
