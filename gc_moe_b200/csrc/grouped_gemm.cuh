@@ -127,7 +127,7 @@ struct RoleTimer {
 };
 
 struct GemmSmemLayout {
-    uint32_t w, a, sfw, sfa, bars, tables, amax, rows, total;
+    uint32_t w, a, sfw, sfa, bars, tables, amax, rows, out, total;
 };
 
 __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint32_t block_m,
@@ -144,7 +144,8 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
     l.tables = l.bars + (2 * stages + 6) * 8 + 16;
     l.amax = l.tables + round_up_u32((2 * local_experts + 1) * 4, 16);
     l.rows = l.amax + 2 * 4 * 16 * 4;                 // amax exchange [2][4][16] floats
-    l.total = l.rows + 2 * block_m * 16;              // per-block row info, double buffered
+    l.out = round_up_u32(l.rows + 2 * block_m * 16, 16);   // per-block row info, double buffered
+    l.total = l.out + 2 * 16 * kHalfRows * 2;          // output transpose: [2][16 tokens][128 channels] bf16
     return l;
 }
 
@@ -237,6 +238,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     int* const tbl_count = tbl_start + p.local_experts + 1;               // [E_loc]
     float* const amax_x = reinterpret_cast<float*>(gbase + L.amax);       // [2][4][16]
     uint32_t* const row_info = reinterpret_cast<uint32_t*>(gbase + L.rows);  // [2][BM][4]
+    __nv_bfloat16* const out_stage = reinterpret_cast<__nv_bfloat16*>(gbase + L.out);  // [2][16][128]
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -490,17 +492,27 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                 __uint_as_float(vi[c]);
                     }
                 } else if constexpr (kPhase == kPhaseL2) {
+                    // Transpose through shared memory so that a token's 128 channels leave
+                    // as 16-byte vectors: 256 contiguous bytes per half-warp, which is what
+                    // NVLink (and HBM) want, instead of 2-byte elements per lane.
+                    __nv_bfloat16* const tile = out_stage + xbuf * 16 * kHalfRows;
 #pragma unroll
-                    for (uint32_t c = 0; c < 16; ++c) {
+                    for (uint32_t c = 0; c < 16; ++c)
+                        tile[c * kHalfRows + r] = __float2bfloat16_rn(__uint_as_float(vi[c]));
+                    epilogue_barrier();
+#pragma unroll
+                    for (uint32_t v = 0; v < 2; ++v) {
+                        const uint32_t c = (etid >> 4) + v * 8, seg = etid & 15u;
                         const uint32_t col = c0 + c;
                         if (col < valid) {
                             const uint32_t src_rank = info[col * 3], src_token = info[col * 3 + 1], slot = info[col * 3 + 2];
-                            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.combine_base[src_rank]) +
-                                (static_cast<size_t>(slot) * p.capacity + src_token) * p.hidden +
-                                nh * kHalfRows + r;
-                            *dst = __float2bfloat16_rn(__uint_as_float(vi[c]));
+                            uint4* dst = reinterpret_cast<uint4*>(
+                                reinterpret_cast<__nv_bfloat16*>(p.combine_base[src_rank]) +
+                                (static_cast<size_t>(slot) * p.capacity + src_token) * p.hidden + nh * kHalfRows) + seg;
+                            *dst = *reinterpret_cast<const uint4*>(tile + c * kHalfRows + seg * 8);
                         }
                     }
+                    xbuf ^= 1u;
                 } else {
                     // Rows come in groups of 16: 8 gate rows then the 8 up rows of the
                     // same channels, so lane l and lane l^8 hold a channel's pair.  The
