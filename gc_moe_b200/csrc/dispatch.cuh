@@ -54,6 +54,7 @@ struct DispatchParams {
     int* expert_count;            // [E_loc]
     int* expert_block_start;      // [E_loc + 1]
     uint32_t* call_info;          // [kCallInfoWords]
+    int* shared_table;            // fused shared expert: {tokens, 0, row blocks}, or null
     int* stats;                   // optional cumulative per-expert counter (may be null)
     uint32_t* status;
     uint64_t timeout_ns;
@@ -225,6 +226,11 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             p.call_info[kCallGeneration] = gen;
             p.call_info[kCallCombineRows] = misc[2];
             p.call_info[kCallEpoch] = epoch;
+            if (p.shared_table != nullptr) {
+                p.shared_table[0] = static_cast<int>(p.num_tokens);
+                p.shared_table[1] = 0;
+                p.shared_table[2] = static_cast<int>((p.num_tokens + p.block_m - 1) / p.block_m);
+            }
         }
     }
 

@@ -121,8 +121,10 @@ static int check_problem(const gcmoe_problem& q) {
     const long long routes = 1ll * q.num_ranks * q.capacity * (q.topk < local ? q.topk : local);
     if (q.ring_tokens < routes + local * (bm - 1))
         return fail(GCMOE_ERR_UNSUPPORTED, "ring of %d rows cannot hold the whole receive pool", q.ring_tokens);
-    if (q.num_shared_experts != 0)
-        return fail(GCMOE_ERR_UNSUPPORTED, "the fused shared expert is not built into this library version");
+    if (q.num_shared_experts < 0 || (q.num_shared_experts > 0 && q.shared_gran_k != 32 && q.shared_gran_k != 128))
+        return fail(GCMOE_ERR_INVALID, "invalid shared expert configuration");
+    if (1ll * q.num_shared_experts * q.intermediate > 65536)
+        return fail(GCMOE_ERR_UNSUPPORTED, "shared intermediate size too large");
     return GCMOE_OK;
 }
 
@@ -133,7 +135,7 @@ extern "C" const char* gcmoe_last_error(void) { return g_error; }
 extern "C" size_t gcmoe_scratch_bytes(const gcmoe_problem* problem) {
     if (problem == nullptr || problem->num_ranks <= 0) return 0;
     const size_t local = size_t(problem->num_experts / problem->num_ranks);
-    return round_up_u32(uint32_t(kStatusWords * 4 + (2 * local + 1) * 4 + kCallInfoWords * 4), 256);
+    return round_up_u32(uint32_t(kStatusWords * 4 + (2 * local + 1) * 4 + kCallInfoWords * 4 + 3 * 4), 256);
 }
 
 extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
@@ -156,6 +158,13 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         return fail(GCMOE_ERR_INVALID, "weight scales must be MN-major with a 4-aligned K stride");
     if (b.scratch == 0 || b.scratch % 16 || b.scratch_bytes < gcmoe_scratch_bytes(problem))
         return fail(GCMOE_ERR_INVALID, "scratch block missing or too small");
+    if (q.num_shared_experts > 0) {
+        if (b.sw1 == 0 || b.sw2 == 0 || b.sw1_sf == 0 || b.sw2_sf == 0 || b.sw1 % 16 || b.sw2 % 16 ||
+            b.sw1_sf % 16 || b.sw2_sf % 16 || b.sw1_sf_stride % 4 || b.sw2_sf_stride % 4 ||
+            b.sw1_sf_stride < uint64_t(2) * q.num_shared_experts * q.intermediate ||
+            b.sw2_sf_stride < uint64_t(q.hidden) || b.shared_sf_rows == 0)
+            return fail(GCMOE_ERR_INVALID, "shared expert weights, scales or scale views missing or misaligned");
+    }
     if (q.num_ranks > 1) {
         for (int r = 0; r < q.num_ranks; ++r)
             if (b.arena_base[r] == 0 || b.arena_base[r] % 16)
@@ -233,92 +242,149 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     if (plan->dispatch_smem > uint32_t(kSmemLimit))
         return bail(fail(GCMOE_ERR_UNSUPPORTED, "dispatch slice does not fit shared memory"));
 
-    // ---- the two grouped GEMMs
-    const uint32_t stages = gemm_pick_stages(bm, sfbm, EL);
+    // ---- the two grouped GEMMs (each: shared-expert segment first, then routed)
+    const uint32_t S = q.num_shared_experts, IS = S * I;
+    const uint32_t table_words = (2 * EL + 1) + (S ? 3 : 0);
+    const uint32_t stages = gemm_pick_stages(bm, sfbm, table_words);
     if (stages < 2) return bail(fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm));
-    plan->gemm_smem = gemm_smem_layout(stages, bm, sfbm, EL).total + 1024;
+    plan->gemm_smem = gemm_smem_layout(stages, bm, sfbm, table_words).total + 1024;
     // Two accumulator stages (epilogue overlaps the next tile) while they fit TMEM.
     const uint32_t acc_stages = gemm_tmem_columns(bm, sfbm, 2) <= 512 ? 2u : 1u;
     if (gemm_tmem_columns(bm, sfbm, acc_stages) > 512)
         return bail(fail(GCMOE_ERR_UNSUPPORTED, "TMEM budget exceeded"));
 
-    auto fill_common = [&](GemmParams& g, uint32_t w_rows, uint32_t k) {
+    auto fill_common = [&](GemmParams& g) {
         memset(&g, 0, sizeof(g));
-        g.expert_block_start = expert_block_start;
-        g.expert_count = expert_count;
         g.status = plan->status;
         g.timeout_ns = timeout_ns;
-        g.w_rows = w_rows;
-        g.k_blocks = k / 128;
-        g.n_tiles = w_rows / kTileRows;
         g.block_m = bm;
         g.sf_block_m = sfbm;
         g.stages = stages;
-        g.local_experts = EL;
-        g.weight_format = 5;
-        g.weight_tx_bytes = kTileRows * 128 / 2;
         g.acc_stages = acc_stages;
+        g.table_words = table_words;
         g.tmem_cols = pow2_at_least(gemm_tmem_columns(bm, sfbm, acc_stages));
-        g.act_sf_stride = q.sf_ring_tokens;
+        g.clamp = q.clamp;
+        g.has_clamp = q.has_clamp != 0;
+        g.fast_math = q.fast_math != 0;
         g.capacity = q.capacity;
         g.hidden = H;
-        g.inter = I;
+        g.topk = q.topk;
+        g.rank = q.rank;
         g.num_ranks = P;
         g.call_info = call_info;
         g.rows_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kRowsArrived);
-        for (uint32_t r = 0; r < P; ++r)
+        for (uint32_t r = 0; r < P; ++r) {
             g.combine_arrived[r] = b.arena_base[r] + b.off_exchange + exchange::kCombineArrived;
+            g.combine_base[r] = b.arena_base[r] + b.off_combine_tokens;
+        }
     };
-    auto encode_pair = [&](GemmParams& g, uint64_t acts, uint32_t k, uint64_t weights, uint32_t w_rows,
-                           const char* what) -> int {
+    // Routed experts: FP4 weights [EL][K/128][rows][64 B], pool rows as activations.
+    auto routed_segment = [&](GemmSegment& sg, uint64_t acts, uint64_t acts_sf, uint32_t k, uint64_t weights,
+                              uint64_t w_sf, uint64_t w_sf_stride, uint32_t w_rows, const char* what) -> int {
+        sg.tile_start = expert_block_start;
+        sg.count = expert_count;
+        sg.experts = EL;
+        sg.w_rows = w_rows;
+        sg.k_blocks = k / 128;
+        sg.n_tiles = w_rows / kTileRows;
+        sg.weight_format = 5;
+        sg.weight_tx_bytes = kTileRows * 128 / 2;
+        sg.w_sf_kblocks = 1;
+        sg.act_sf = reinterpret_cast<const uint32_t*>(acts_sf);
+        sg.act_sf_stride = q.sf_ring_tokens;
+        sg.w_sf = reinterpret_cast<const uint32_t*>(w_sf);
+        sg.w_sf_stride = uint32_t(w_sf_stride);
         const uint64_t adims[2] = {k, uint64_t(q.ring_tokens)};
         const uint64_t astr[1] = {k};
         const uint32_t abox[2] = {128, bm};
-        if (int rc = encode_map(&g.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
+        if (int rc = encode_map(&sg.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
             return rc;
-        // FP4 weights: 128-element (64-byte) rows of one K128 tile are adjacent,
-        // so a 128 x 256 box is one contiguous 16 KiB range in HBM.
+        // 128-element (64-byte) rows of one K128 tile are adjacent, so a 128 x 256
+        // box is one contiguous 16 KiB range in HBM.
         const uint64_t wdims[4] = {128, w_rows, k / 128, EL};
         const uint64_t wstr[3] = {64, uint64_t(w_rows) * 64, uint64_t(w_rows) * 64 * (k / 128)};
         const uint32_t wbox[4] = {128, kTileRows, 1, 1};
-        return encode_map(&g.tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, weights, wdims, wstr, wbox, what);
+        return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, weights, wdims, wstr, wbox, what);
+    };
+    // Shared expert: FP8 weights [K/128][rows][128 B], this rank's own tokens as rows.
+    int* shared_table = reinterpret_cast<int*>(call_info + kCallInfoWords);   // count, start[0], start[1]
+    auto shared_segment = [&](GemmSegment& sg, uint64_t acts, uint64_t acts_sf, uint32_t k, uint64_t weights,
+                              uint64_t w_sf, uint64_t w_sf_stride, uint32_t w_rows, const char* what) -> int {
+        sg.shared = 1;
+        sg.count = shared_table;
+        sg.tile_start = shared_table + 1;
+        sg.experts = 1;
+        sg.w_rows = w_rows;
+        sg.k_blocks = k / 128;
+        sg.n_tiles = w_rows / kTileRows;
+        sg.weight_format = 0;
+        sg.weight_tx_bytes = kTileRows * 128;
+        sg.w_sf_kblocks = q.shared_gran_k == 128 ? 4 : 1;
+        sg.act_sf = reinterpret_cast<const uint32_t*>(acts_sf);
+        sg.act_sf_stride = uint32_t(b.shared_sf_rows);
+        sg.w_sf = reinterpret_cast<const uint32_t*>(w_sf);
+        sg.w_sf_stride = uint32_t(w_sf_stride);
+        const uint64_t adims[2] = {k, uint64_t(q.capacity)};
+        const uint64_t astr[1] = {k};
+        const uint32_t abox[2] = {128, bm};
+        if (int rc = encode_map(&sg.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
+            return rc;
+        const uint64_t wdims[3] = {128, w_rows, k / 128};
+        const uint64_t wstr[2] = {128, uint64_t(w_rows) * 128};
+        const uint32_t wbox[3] = {128, kTileRows, 1};
+        return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, weights, wdims, wstr, wbox, what);
     };
 
     GemmParams& g1 = plan->l1;
-    fill_common(g1, 2 * I, H);
-    if (int rc = encode_pair(g1, arena + b.off_l1_acts, H, b.w1, 2 * I, "gate/up GEMM")) return bail(rc);
-    g1.act_sf = reinterpret_cast<const uint32_t*>(arena + b.off_l1_acts_sf);
-    g1.w_sf = reinterpret_cast<const uint32_t*>(b.w1_sf);
-    g1.w_sf_stride = uint32_t(b.w1_sf_stride);
-    g1.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts);
-    g1.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts_sf);
-    g1.out_sf_stride = q.sf_ring_tokens;
-    g1.route_weight = reinterpret_cast<const float*>(arena + b.off_l1_topk_weights);
-    g1.clamp = q.clamp;
-    g1.has_clamp = q.has_clamp != 0;
-    g1.fast_math = q.fast_math != 0;
-
     GemmParams& g2 = plan->l2;
-    fill_common(g2, H, I);
-    if (int rc = encode_pair(g2, arena + b.off_l2_acts, I, b.w2, H, "down GEMM")) return bail(rc);
-    g2.act_sf = reinterpret_cast<const uint32_t*>(arena + b.off_l2_acts_sf);
-    g2.w_sf = reinterpret_cast<const uint32_t*>(b.w2_sf);
-    g2.w_sf_stride = uint32_t(b.w2_sf_stride);
-    g2.metadata = reinterpret_cast<const uint32_t*>(arena + b.off_metadata);
-    for (uint32_t r = 0; r < P; ++r) g2.combine_base[r] = b.arena_base[r] + b.off_combine_tokens;
+    fill_common(g1);
+    fill_common(g2);
+    uint32_t nseg = 0;
+    if (S) {
+        GemmSegment& s1 = g1.seg[0];
+        if (int rc = shared_segment(s1, arena + b.off_x, arena + b.off_shared_l1_acts_sf, H, b.sw1, b.sw1_sf,
+                                    b.sw1_sf_stride, 2 * IS, "shared gate/up GEMM")) return bail(rc);
+        s1.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_shared_l2_acts);
+        s1.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_shared_l2_acts_sf);
+        s1.out_sf_stride = uint32_t(b.shared_sf_rows);
+        s1.inter = IS;
+        GemmSegment& s2 = g2.seg[0];
+        if (int rc = shared_segment(s2, arena + b.off_shared_l2_acts, arena + b.off_shared_l2_acts_sf, IS, b.sw2,
+                                    b.sw2_sf, b.sw2_sf_stride, H, "shared down GEMM")) return bail(rc);
+        nseg = 1;
+    }
+    {
+        GemmSegment& r1 = g1.seg[nseg];
+        if (int rc = routed_segment(r1, arena + b.off_l1_acts, arena + b.off_l1_acts_sf, H, b.w1, b.w1_sf,
+                                    b.w1_sf_stride, 2 * I, "gate/up GEMM")) return bail(rc);
+        r1.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts);
+        r1.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts_sf);
+        r1.out_sf_stride = q.sf_ring_tokens;
+        r1.inter = I;
+        r1.route_weight = reinterpret_cast<const float*>(arena + b.off_l1_topk_weights);
+        GemmSegment& r2 = g2.seg[nseg];
+        if (int rc = routed_segment(r2, arena + b.off_l2_acts, arena + b.off_l2_acts_sf, I, b.w2, b.w2_sf,
+                                    b.w2_sf_stride, H, "down GEMM")) return bail(rc);
+        r2.metadata = reinterpret_cast<const uint32_t*>(arena + b.off_metadata);
+        ++nseg;
+    }
+    g1.num_segments = g2.num_segments = nseg;
+    d.shared_table = S ? shared_table : nullptr;
 
     // Upper bound of pool blocks this call can produce: one partial block per
     // expert that can be hit, plus the full blocks.
     const uint64_t all_routes = uint64_t(P) * routes;   // collective calls bring the same order of T
     uint64_t max_blocks = (all_routes < EL ? all_routes : EL) + all_routes / bm;
     if (max_blocks < 1) max_blocks = 1;
-    auto grid_for = [&](uint32_t n_tiles) {
+    const uint64_t shared_blocks = S ? (uint64_t(q.num_tokens) + bm - 1) / bm : 0;
+    auto grid_for = [&](const GemmParams& g) {
         // With several ranks the pool depends on what the other ranks send.
-        const uint64_t tiles = P > 1 ? uint64_t(plan->num_sms) : max_blocks * n_tiles;
+        const uint64_t tiles = P > 1 ? uint64_t(plan->num_sms)
+            : max_blocks * g.seg[g.num_segments - 1].n_tiles + (S ? shared_blocks * g.seg[0].n_tiles : 0);
         return uint32_t(tiles < uint64_t(plan->num_sms) ? tiles : uint64_t(plan->num_sms));
     };
-    plan->gemm_grid_l1 = grid_for(g1.n_tiles);
-    plan->gemm_grid_l2 = grid_for(g2.n_tiles);
+    plan->gemm_grid_l1 = grid_for(g1);
+    plan->gemm_grid_l2 = grid_for(g2);
 
     // ---- combine
     CombineParams& c = plan->combine;
@@ -328,7 +394,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     c.y = reinterpret_cast<__nv_bfloat16*>(b.y);
     c.epoch_word = reinterpret_cast<uint32_t*>(arena + b.off_recv_parity);
     c.num_tokens = q.num_tokens; c.topk = q.topk; c.hidden = H; c.capacity = q.capacity;
-    c.num_experts = E; c.has_shared = 0;
+    c.num_experts = E; c.has_shared = S ? 1 : 0;
     c.num_ranks = P;
     c.call_info = call_info;
     c.combine_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kCombineArrived);
@@ -424,7 +490,7 @@ namespace gcmoe {
 
 constexpr int kStaticMaxLocalExperts = 128;
 constexpr size_t kStaticScratchBytes = 1280;   // status + counts + prefix for 128 local experts, 256-aligned
-static_assert(kStaticScratchBytes >= kStatusWords * 4 + (2 * kStaticMaxLocalExperts + 1) * 4 + kCallInfoWords * 4, "static scratch too small");
+static_assert(kStaticScratchBytes >= kStatusWords * 4 + (2 * kStaticMaxLocalExperts + 1) * 4 + kCallInfoWords * 4 + 12, "static scratch too small");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 

@@ -55,47 +55,63 @@ constexpr int kSmemLimit = 232448;         // opt-in dynamic shared memory per C
 
 enum GemmPhase : int { kPhaseL1 = 0, kPhaseL2 = 1, kPhaseRaw = 2 };
 
-struct GemmParams {
+// One grouped problem of a launch: the routed experts of this rank, or the
+// fused shared expert (one "expert" whose rows are this rank's own tokens,
+// FP8 weights).  A launch runs the shared segment's tiles first -- they depend
+// on nothing another GPU sends, so they hide the dispatch exchange -- and the
+// routed segment's after them.
+struct GemmSegment {
     CUtensorMap tm_act;     // u8 [rows][K], box 128 x BM, 128-byte swizzle
     CUtensorMap tm_w;       // FP4: 16U4_ALIGN16B [E][K/128][rows][128], box 128 x 256
-                            // FP8: u8 [K/128][rows][128]
+                            // FP8: u8 [K/128][rows][128], box 128 x 256
     const uint32_t* act_sf;  // packed scale words, MN-major: word (kb, r) at kb * act_sf_stride + r
-    const uint32_t* w_sf;    // word (e, kb, row) at (e * k_blocks + kb) * w_sf_stride + row
-    const int* expert_block_start;  // [local_experts + 1] pool-block prefix
-    const int* expert_count;        // [local_experts] tokens per local expert
-    uint32_t* status;
-    uint64_t timeout_ns;
+    const uint32_t* w_sf;    // word (e, plane, row) at (e * planes + plane) * w_sf_stride + row
+    const int* tile_start;   // [experts + 1] prefix of the experts' row blocks
+    const int* count;        // [experts] rows per expert
     uint32_t act_sf_stride;  // words between consecutive K128 planes of act_sf
-    uint32_t w_sf_stride;    // words between consecutive K128 planes of w_sf
+    uint32_t w_sf_stride;    // words between consecutive planes of w_sf
+    uint32_t w_sf_kblocks;   // K128 blocks one w_sf word covers: 1 (K32 scales) or 4 (K128 scales)
     uint32_t w_rows;         // weight rows per expert (2I for the gate/up GEMM, H for the down GEMM)
     uint32_t k_blocks;       // K / 128
     uint32_t n_tiles;        // w_rows / 256
-    uint32_t block_m;        // BM
-    uint32_t sf_block_m;     // BM rounded up to 128 (scale rows reserved per pool block)
-    uint32_t stages;
-    uint32_t acc_stages;     // 2, or 1 when two accumulator stages exceed TMEM
-    uint32_t local_experts;
+    uint32_t experts;
     uint32_t weight_format;  // 5 = e2m1 (FP4), 0 = e4m3
     uint32_t weight_tx_bytes;  // bytes the weight tile's TMA reports to the stage barrier
-    uint32_t tmem_cols;
+    uint32_t shared;         // rows are own tokens: no route weight, no arrival wait, output slot = topk
     // ---- gate/up epilogue (kPhaseL1)
     uint8_t* out_acts;        // e4m3 [rows][I]
     uint8_t* out_sf;          // bytes of the MN-major packed scale ring
-    const float* route_weight;  // [rows]
+    const float* route_weight;  // [rows], unused for the shared segment
     uint32_t out_sf_stride;   // words between K128 planes of out_sf
-    uint32_t inter;           // I
+    uint32_t inter;           // row length of out_acts
+    // ---- down epilogue (kPhaseL2)
+    const uint32_t* metadata;  // (src_rank, src_token, slot) per pool row, unused for the shared segment
+};
+
+struct GemmParams {
+    GemmSegment seg[2];
+    uint32_t num_segments;
+    uint32_t* status;
+    uint64_t timeout_ns;
+    uint32_t block_m;        // BM
+    uint32_t sf_block_m;     // BM rounded up to 128 (scale rows reserved per row block)
+    uint32_t stages;
+    uint32_t acc_stages;     // 2, or 1 when two accumulator stages exceed TMEM
+    uint32_t table_words;    // shared-memory words for the segments' tables
+    uint32_t tmem_cols;
     float clamp;
     uint32_t has_clamp;
     uint32_t fast_math;
-    // ---- down epilogue (kPhaseL2)
-    const uint32_t* metadata;  // (src_rank, src_token, slot) per pool row
+    // ---- down epilogue
     uint64_t combine_base[kMaxRanks];  // address of combine_tokens on each rank
     uint32_t capacity;
     uint32_t hidden;
-    // ---- raw epilogue (kPhaseRaw): FP32 accumulators, [rows][w_rows]
+    uint32_t topk;
+    uint32_t rank;
+    // ---- raw epilogue (kPhaseRaw): FP32 accumulators of segment 0, [rows][w_rows]
     float* raw_out;
     // ---- multi-rank: arrival counters of the dispatched rows (gate/up) and of
-    // the combine contributions (down); null / 1 on a single rank
+    // the combine contributions (down); unused on a single rank
     const uint32_t* call_info;        // [kCallInfoWords] written by the dispatch kernel
     const uint32_t* rows_arrived;     // this rank's exchange::kRowsArrived, [2][kMaxLocalExperts]
     uint64_t combine_arrived[kMaxRanks];  // address of exchange::kCombineArrived on each rank
@@ -132,7 +148,7 @@ struct GemmSmemLayout {
 
 __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint32_t block_m,
                                                            uint32_t sf_block_m,
-                                                           uint32_t local_experts) {
+                                                           uint32_t table_words) {
     GemmSmemLayout l;
     l.w = 0;
     l.a = l.w + stages * kWeightStageBytes;
@@ -142,7 +158,7 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
     // full[stages], empty[stages], acc_full[2], acc_empty[2], drain[2], then the
     // TMEM base slot and the abort word
     l.tables = l.bars + (2 * stages + 6) * 8 + 16;
-    l.amax = l.tables + round_up_u32((2 * local_experts + 1) * 4, 16);
+    l.amax = l.tables + round_up_u32(table_words * 4, 16);
     l.rows = l.amax + 2 * 4 * 16 * 4;                 // amax exchange [2][4][16] floats
     l.out = round_up_u32(l.rows + 2 * block_m * 16, 16);   // per-block row info, double buffered
     l.total = l.out + 2 * 16 * kHalfRows * 2;          // output transpose: [2][16 tokens][128 channels] bf16
@@ -150,9 +166,9 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
 }
 
 __host__ inline uint32_t gemm_pick_stages(uint32_t block_m, uint32_t sf_block_m,
-                                          uint32_t local_experts) {
+                                          uint32_t table_words) {
     for (uint32_t s = kMaxStages; s >= 2; --s) {
-        if (gemm_smem_layout(s, block_m, sf_block_m, local_experts).total + 1024 <= kSmemLimit)
+        if (gemm_smem_layout(s, block_m, sf_block_m, table_words).total + 1024 <= kSmemLimit)
             return s;
     }
     return 0;
@@ -218,6 +234,12 @@ struct StageCursor {
     }
 };
 
+// Where a tile of the launch's work list lives: which segment, which row block
+// of which expert, which 256-row slice of the expert's weights.
+struct TileCoord {
+    uint32_t seg, block, n_tile, expert, valid;
+};
+
 template <int kPhase>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
@@ -226,7 +248,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t base = (raw_addr + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
     uint8_t* const gbase = smem_raw + (base - raw_addr);
 
-    const GemmSmemLayout L = gemm_smem_layout(p.stages, p.block_m, p.sf_block_m, p.local_experts);
+    const GemmSmemLayout L = gemm_smem_layout(p.stages, p.block_m, p.sf_block_m, p.table_words);
     const uint32_t bar_full = base + L.bars;
     const uint32_t bar_empty = bar_full + p.stages * 8;
     const uint32_t bar_acc_full = bar_empty + p.stages * 8;
@@ -234,8 +256,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t bar_drain = bar_acc_empty + 16;
     volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + L.bars + (2 * p.stages + 6) * 8);
     volatile uint32_t* const abort_word = tmem_slot + 1;
-    int* const tbl_start = reinterpret_cast<int*>(gbase + L.tables);      // [E_loc + 1]
-    int* const tbl_count = tbl_start + p.local_experts + 1;               // [E_loc]
+    int* const tables = reinterpret_cast<int*>(gbase + L.tables);
     float* const amax_x = reinterpret_cast<float*>(gbase + L.amax);       // [2][4][16]
     uint32_t* const row_info = reinterpret_cast<uint32_t*>(gbase + L.rows);  // [2][BM][4]
     __nv_bfloat16* const out_stage = reinterpret_cast<__nv_bfloat16*>(gbase + L.out);  // [2][16][128]
@@ -261,13 +282,20 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         *abort_word = 0;
         ptx::fence_mbar_init();
-        ptx::prefetch_tensormap(&p.tm_act);
-        ptx::prefetch_tensormap(&p.tm_w);
+        for (uint32_t g = 0; g < p.num_segments; ++g) {
+            ptx::prefetch_tensormap(&p.seg[g].tm_act);
+            ptx::prefetch_tensormap(&p.seg[g].tm_w);
+        }
     }
-    for (uint32_t i = threadIdx.x; i <= p.local_experts; i += kGemmThreads)
-        tbl_start[i] = p.expert_block_start[i];
-    for (uint32_t i = threadIdx.x; i < p.local_experts; i += kGemmThreads)
-        tbl_count[i] = p.expert_count[i];
+    // Tables of both segments: [start (experts + 1) | count (experts)] each.
+    const uint32_t experts0 = p.seg[0].experts;
+    auto tbl_start = [&](uint32_t g) -> int* { return tables + (g ? 2 * experts0 + 1 : 0); };
+    auto tbl_count = [&](uint32_t g) -> int* { return tbl_start(g) + p.seg[g].experts + 1; };
+    for (uint32_t g = 0; g < p.num_segments; ++g) {
+        const uint32_t ne = p.seg[g].experts;
+        for (uint32_t i = threadIdx.x; i <= ne; i += kGemmThreads) tbl_start(g)[i] = p.seg[g].tile_start[i];
+        for (uint32_t i = threadIdx.x; i < ne; i += kGemmThreads) tbl_count(g)[i] = p.seg[g].count[i];
+    }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), p.tmem_cols);
         ptx::tmem_relinquish();
@@ -277,49 +305,59 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t pool_blocks = static_cast<uint32_t>(tbl_start[p.local_experts]);
-    const uint32_t total_tiles = pool_blocks * p.n_tiles;
     const uint32_t bm = p.block_m;
+    const uint32_t tiles0 = static_cast<uint32_t>(tbl_start(0)[p.seg[0].experts]) * p.seg[0].n_tiles;
+    const uint32_t tiles1 = p.num_segments > 1
+        ? static_cast<uint32_t>(tbl_start(1)[p.seg[1].experts]) * p.seg[1].n_tiles : 0u;
+    const uint32_t total_tiles = tiles0 + tiles1;
 
-    // Local expert that owns pool block b: last l with start[l] <= b.
-    auto expert_of_block = [&](uint32_t b) -> uint32_t {
-        uint32_t lo = 0, hi = p.local_experts;   // start[lo] <= b < start[hi]
+    // Decode a tile index: segment, row block, 256-row weight slice, owning
+    // expert (last e with start[e] <= block) and the block's valid rows.
+    auto locate = [&](uint32_t tile) -> TileCoord {
+        TileCoord c;
+        c.seg = tile >= tiles0 ? 1u : 0u;
+        const uint32_t local = tile - (c.seg ? tiles0 : 0u);
+        const uint32_t nt = p.seg[c.seg].n_tiles;
+        c.block = local / nt;
+        c.n_tile = local - c.block * nt;
+        const int* const start = tbl_start(c.seg);
+        uint32_t lo = 0, hi = p.seg[c.seg].experts;   // start[lo] <= block < start[hi]
         while (hi - lo > 1) {
             const uint32_t mid = (lo + hi) >> 1;
-            if (static_cast<uint32_t>(tbl_start[mid]) <= b) lo = mid; else hi = mid;
+            if (static_cast<uint32_t>(start[mid]) <= c.block) lo = mid; else hi = mid;
         }
-        return lo;
-    };
-    auto valid_rows = [&](uint32_t b, uint32_t e) -> uint32_t {
-        const uint32_t left = static_cast<uint32_t>(tbl_count[e]) - (b - static_cast<uint32_t>(tbl_start[e])) * bm;
-        return left < bm ? left : bm;
+        c.expert = lo;
+        const uint32_t left = static_cast<uint32_t>(tbl_count(c.seg)[lo]) - (c.block - static_cast<uint32_t>(start[lo])) * bm;
+        c.valid = left < bm ? left : bm;
+        return c;
     };
 
     if (warp == 0 || warp == 2) {
         // ------------------------------------------------------------ producers
         const bool weights = warp == 0;
-        const uint32_t tx = weights ? p.weight_tx_bytes + kWeightSfStageBytes : bm * kTileK + p.sf_block_m * 4;
         StageCursor cur;
         uint32_t armed = 0, armed_parity = 0, ntiles = 0, ready_expert = 0xFFFFFFFFu;
         bool ok = true;
         RoleTimer timer(p.timing, weights ? 0 : 1);
         for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++ntiles) {
-            const uint32_t b = tile / p.n_tiles, nt = tile - b * p.n_tiles;
-            const uint32_t e = expert_of_block(b);
-            const uint32_t* wsf = p.w_sf + static_cast<size_t>(e) * p.k_blocks * p.w_sf_stride + nt * kTileRows;
-            const uint32_t* asf = p.act_sf + static_cast<size_t>(b) * p.sf_block_m;
-            if (kPhase != kPhaseL2 && !weights && p.num_ranks > 1 && e != ready_expert) {
+            const TileCoord tc = locate(tile);
+            const GemmSegment& sg = p.seg[tc.seg];
+            const uint32_t b = tc.block, nt = tc.n_tile, e = tc.expert;
+            const uint32_t sf_planes = (sg.k_blocks + sg.w_sf_kblocks - 1) / sg.w_sf_kblocks;
+            const uint32_t* wsf = sg.w_sf + static_cast<size_t>(e) * sf_planes * sg.w_sf_stride + nt * kTileRows;
+            const uint32_t* asf = sg.act_sf + static_cast<size_t>(b) * p.sf_block_m;
+            if (kPhase != kPhaseL2 && !weights && p.num_ranks > 1 && !sg.shared && e != ready_expert) {
                 // The rows of this expert are pushed by other GPUs: wait until all of
                 // them have landed, then order the TMA (async proxy) after the acquire.
                 uint32_t landed = 1;
                 if (lane == 0)
                     landed = flag_wait_eq(p.rows_arrived + p.call_info[kCallGeneration] * kMaxLocalExperts + e,
-                                          static_cast<uint32_t>(tbl_count[e]), ctl, 5);
+                                          static_cast<uint32_t>(tbl_count(tc.seg)[e]), ctl, 5);
                 if (!__shfl_sync(0xffffffffu, landed, 0)) { ok = false; break; }
                 ptx::fence_proxy_async_global();
                 ready_expert = e;
             }
-            for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+            for (uint32_t kb = 0; kb < sg.k_blocks; ++kb) {
                 timer.start();
                 const bool got = mbar_wait(bar_empty + 8 * cur.stage, cur.phase ^ 1u, ctl, 1);
                 timer.stop_a();
@@ -328,22 +366,26 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 armed |= 1u << cur.stage;
                 armed_parity = (armed_parity & ~(1u << cur.stage)) | (cur.phase << cur.stage);
                 if (ptx::elect_one()) {
-                    ptx::mbar_arrive_expect_tx(full, tx);
                     if (weights) {
-                        if (p.weight_format == 5u)
-                            ptx::tma_load_4d(base + L.w + cur.stage * kWeightStageBytes, &p.tm_w, full, 0,
+                        // K128-granular scales: one packed word serves four K128 blocks
+                        const bool load_sf = kb % sg.w_sf_kblocks == 0;
+                        ptx::mbar_arrive_expect_tx(full, sg.weight_tx_bytes + (load_sf ? kWeightSfStageBytes : 0));
+                        if (sg.weight_format == 5u)
+                            ptx::tma_load_4d(base + L.w + cur.stage * kWeightStageBytes, &sg.tm_w, full, 0,
                                              nt * kTileRows, kb, e, ptx::kEvictFirst);
                         else
-                            ptx::tma_load_3d(base + L.w + cur.stage * kWeightStageBytes, &p.tm_w, full, 0,
+                            ptx::tma_load_3d(base + L.w + cur.stage * kWeightStageBytes, &sg.tm_w, full, 0,
                                              nt * kTileRows, kb, ptx::kEvictFirst);
-                        ptx::bulk_load_1d(base + L.sfw + cur.stage * kWeightSfStageBytes,
-                                          wsf + static_cast<size_t>(kb) * p.w_sf_stride, kWeightSfStageBytes,
-                                          full, ptx::kEvictFirst);
+                        if (load_sf)
+                            ptx::bulk_load_1d(base + L.sfw + cur.stage * kWeightSfStageBytes,
+                                              wsf + static_cast<size_t>(kb / sg.w_sf_kblocks) * sg.w_sf_stride,
+                                              kWeightSfStageBytes, full, ptx::kEvictFirst);
                     } else {
-                        ptx::tma_load_2d(base + L.a + cur.stage * bm * kTileK, &p.tm_act, full, kb * kTileK,
+                        ptx::mbar_arrive_expect_tx(full, bm * kTileK + p.sf_block_m * 4);
+                        ptx::tma_load_2d(base + L.a + cur.stage * bm * kTileK, &sg.tm_act, full, kb * kTileK,
                                          b * bm, ptx::kEvictLast);
                         ptx::bulk_load_1d(base + L.sfa + cur.stage * p.sf_block_m * 4,
-                                          asf + static_cast<size_t>(kb) * p.act_sf_stride,
+                                          asf + static_cast<size_t>(kb) * sg.act_sf_stride,
                                           p.sf_block_m * 4, full, ptx::kEvictLast);
                     }
                 }
@@ -374,10 +416,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             bool ok = true;
             RoleTimer timer(p.timing, 2 + m);
             for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-                const uint32_t b = tile / p.n_tiles;
-                const uint32_t e = expert_of_block(b);
-                const uint32_t n = round_up_u32(valid_rows(b, e), 16);
-                const uint32_t idesc = ptx::instr_desc(n, p.weight_format);
+                const TileCoord tc = locate(tile);
+                const GemmSegment& sg = p.seg[tc.seg];
+                const uint32_t n = round_up_u32(tc.valid, 16);
+                const uint32_t idesc = ptx::instr_desc(n, sg.weight_format);
                 const uint32_t as = p.acc_stages == 2 ? (it & 1u) : 0u;
                 const uint32_t acc_phase = p.acc_stages == 2 ? ((it >> 1) & 1u) : (it & 1u);
                 timer.start();
@@ -386,7 +428,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 if (!acc_free) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (as * 2 + m) * bm;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                for (uint32_t kb = 0; kb < sg.k_blocks; ++kb) {
                     timer.start();
                     const bool got = mbar_wait(bar_full + 8 * cur.stage, cur.phase, ctl, 3);
                     timer.stop_a();
@@ -395,22 +437,28 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     if (ptx::elect_one()) {
                         const uint32_t sfw_s = base + L.sfw + cur.stage * kWeightSfStageBytes + m * kSfChunkBytes;
                         const uint32_t sfa_s = base + L.sfa + cur.stage * p.sf_block_m * 4;
-                        ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
+                        // Weight scales of K128 granularity arrive with every fourth stage and
+                        // stay in TMEM for the three stages that follow.
+                        if (kb % sg.w_sf_kblocks == 0)
+                            ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
                         ptx::tmem_cp_sf(sfa_tmem, ptx::smem_desc(sfa_s, 128, false));
                         if (p.sf_block_m > 128)
                             ptx::tmem_cp_sf(sfa_tmem + 4, ptx::smem_desc(sfa_s + kSfChunkBytes, 128, false));
                         const uint64_t wdesc = ptx::smem_desc(base + L.w + cur.stage * kWeightStageBytes + m * kHalfStageBytes, 1024, true);
                         const uint64_t adesc = ptx::smem_desc(base + L.a + cur.stage * bm * kTileK, 1024, true);
+                        const uint32_t wide = sg.w_sf_kblocks == 4 ? (kb & 3u) : 0xFFu;
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k) {
-                            // 32 K elements = 32 bytes in the swizzled row = +2 in 16-byte units;
-                            // scale byte k of the stage's packed word for both operands.
+                            // 32 K elements = 32 bytes in the swizzled row = +2 in 16-byte units.
+                            // Scale byte: k-th byte of the stage's packed word (K32 scales), or
+                            // byte kb % 4 of the four-stage word (K128 weight scales).
+                            const uint32_t w_byte = wide == 0xFFu ? k : wide;
                             ptx::mma_mxf8f6f4(d_tmem, wdesc + 2 * k, adesc + 2 * k,
-                                              idesc | (k << 29) | (k << 4), sfw_tmem, sfa_tmem,
+                                              idesc | (w_byte << 29) | (k << 4), sfw_tmem, sfa_tmem,
                                               (kb | k) != 0u ? 1u : 0u);
                         }
                         ptx::tc_commit(bar_empty + 8 * cur.stage);
-                        if (kb + 1 == p.k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
+                        if (kb + 1 == sg.k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
                     }
                     __syncwarp();
                     cur.advance(1, p.stages);
@@ -436,9 +484,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const float clamp_bf16 = __bfloat162float(__float2bfloat16_rn(p.clamp));
         RoleTimer timer(warp == 4 ? p.timing : nullptr, 4);
         for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
-            const uint32_t b = tile / p.n_tiles, nt = tile - b * p.n_tiles;
-            const uint32_t e = expert_of_block(b);
-            const uint32_t valid = valid_rows(b, e);
+            const TileCoord tc = locate(tile);
+            const GemmSegment& sg = p.seg[tc.seg];
+            const uint32_t b = tc.block, nt = tc.n_tile, e = tc.expert, valid = tc.valid;
             const uint32_t ncols = round_up_u32(valid, 16);
             const uint32_t as = p.acc_stages == 2 ? (it & 1u) : 0u;
             const uint32_t acc_phase = p.acc_stages == 2 ? ((it >> 1) & 1u) : (it & 1u);
@@ -446,20 +494,30 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // Stage what the stores need to know about the block's rows while the
             // main loop is still running: route weight (gate/up) or destination.
             uint32_t* const info = row_info + (it & 1u) * bm * 4;
-            if (kPhase == kPhaseL1 && p.num_ranks > 1) {
+            if (kPhase == kPhaseL1 && p.num_ranks > 1 && !sg.shared) {
                 // Route weights are pushed by other GPUs together with the rows.
                 bool landed = true;
                 if (etid == 0)
                     landed = flag_wait_eq(p.rows_arrived + p.call_info[kCallGeneration] * kMaxLocalExperts + e,
-                                          static_cast<uint32_t>(tbl_count[e]), ctl, 6);
+                                          static_cast<uint32_t>(tbl_count(tc.seg)[e]), ctl, 6);
                 if (!all_epilogue_threads(landed)) { ok = false; break; }
             }
             if constexpr (kPhase == kPhaseL1) {
+                // the shared expert's rows carry no route weight
                 for (uint32_t i = etid; i < valid; i += 128)
-                    info[i] = __float_as_uint(p.route_weight[row0 + i]);
+                    info[i] = sg.shared ? __float_as_uint(1.0f) : __float_as_uint(sg.route_weight[row0 + i]);
             } else if constexpr (kPhase == kPhaseL2) {
-                for (uint32_t i = etid; i < valid * 3; i += 128)
-                    info[i] = p.metadata[static_cast<size_t>(row0) * 3 + i];
+                if (sg.shared) {
+                    // own tokens: row t goes to this rank's combine slot `topk`
+                    for (uint32_t i = etid; i < valid; i += 128) {
+                        info[i * 3] = p.rank;
+                        info[i * 3 + 1] = row0 + i;
+                        info[i * 3 + 2] = p.topk;
+                    }
+                } else {
+                    for (uint32_t i = etid; i < valid * 3; i += 128)
+                        info[i] = sg.metadata[static_cast<size_t>(row0) * 3 + i];
+                }
             }
             // Every epilogue thread must take the same exit, or the named barriers
             // below would wait for threads that have left: vote on the outcome.
@@ -488,7 +546,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     for (uint32_t c = 0; c < 16; ++c) {
                         const uint32_t col = c0 + c;
                         if (col < valid)
-                            p.raw_out[static_cast<size_t>(row0 + col) * p.w_rows + nh * kHalfRows + r] =
+                            p.raw_out[static_cast<size_t>(row0 + col) * sg.w_rows + nh * kHalfRows + r] =
                                 __uint_as_float(vi[c]);
                     }
                 } else if constexpr (kPhase == kPhaseL2) {
@@ -552,19 +610,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         const float inv = __uint_as_float((254u - code) << 23);
                         const uint32_t byte = ptx::cvt_e4m3x2(__fmul_rn(res[j], inv), 0.0f) & 0xFFu;
                         if (col < valid) {
-                            p.out_acts[static_cast<size_t>(row0 + col) * p.inter + ch] = static_cast<uint8_t>(byte);
+                            sg.out_acts[static_cast<size_t>(row0 + col) * sg.inter + ch] = static_cast<uint8_t>(byte);
                             if ((q & 1u) == 0u && (lane & 0x17u) == 0u) {
                                 const uint32_t k32 = nh * 2 + (q >> 1);   // index of the 32-channel group
-                                const size_t word = static_cast<size_t>(k32 >> 2) * p.out_sf_stride +
+                                const size_t word = static_cast<size_t>(k32 >> 2) * sg.out_sf_stride +
                                                     static_cast<size_t>(b) * p.sf_block_m + sf_row_in_block(col);
-                                p.out_sf[word * 4 + (k32 & 3u)] = static_cast<uint8_t>(code);
+                                sg.out_sf[word * 4 + (k32 & 3u)] = static_cast<uint8_t>(code);
                             }
                         }
                     }
                     xbuf ^= 1u;
                 }
             }
-            if (kPhase == kPhaseL2 && p.num_ranks > 1) {
+            if (kPhase == kPhaseL2 && p.num_ranks > 1 && !sg.shared) {
                 // Tell each source rank how many of its rows this tile has written
                 // (rows of one source are contiguous in a block).  The barrier orders
                 // every epilogue thread's stores before the leader's release.

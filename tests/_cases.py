@@ -16,7 +16,8 @@ class LayerCase:
     """One world-1 problem: quantised weights on the GPU in operator layout,
     a workspace, and the original CPU tensors for the oracle."""
 
-    def __init__(self, group, num_experts, hidden, inter, topk, capacity=1920, seed=0, weight_std=0.02):
+    def __init__(self, group, num_experts, hidden, inter, topk, capacity=1920, seed=0, weight_std=0.02,
+                 num_shared_experts=0):
         self.e, self.h, self.i, self.k = num_experts, hidden, inter, topk
         self.capacity = capacity
         # Quantise on the GPU (seconds instead of a minute at benchmark sizes);
@@ -32,7 +33,8 @@ class LayerCase:
                 payload[e], codes[e] = quant.quantize_weights_fp4(w)
             gpu.append((payload, codes))
         (self.q1, self.c1), (self.q2, self.c2) = [(a.cpu(), b.cpu()) for a, b in gpu]
-        self.buf = G.get_symm_buffer_for_gc_moe(group, num_experts, capacity, topk, hidden, inter)
+        self.buf = G.get_symm_buffer_for_gc_moe(group, num_experts, capacity, topk, hidden, inter,
+                                                num_shared_experts)
         self.l1, self.l2 = G.transform_weights_for_gc_moe(
             (gpu[0][0], quant.weight_scales_mn_major(gpu[0][1])),
             (gpu[1][0], quant.weight_scales_mn_major(gpu[1][1])))

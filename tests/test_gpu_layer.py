@@ -220,3 +220,54 @@ def test_large_token_regime_with_skewed_routing(large, tokens, expect_bm):
     ref = large.oracle(xq, xsf, idx.to(torch.int64), w.float())
     check_dispatch_products(large.products(tokens, gen), ref.dispatch[0], expect_bm)
     assert_close(y, ref.y[0])
+
+
+def _stage_shared_sf(case, xsf, tokens, bm):
+    """Caller-side staging of the shared expert's input scales: row of token t is
+    (t // BM) * align(BM, 128) + (u // 128) * 128 + (u % 32) * 4 + (u % 128) // 32, u = t % BM
+    (gc_moe/gc/__init__.py:19-23)."""
+    view = case.buf.shared_l1_acts_sf
+    t = torch.arange(tokens)
+    u = t % bm
+    rows = (t // bm) * ((bm + 127) // 128 * 128) + (u // 128) * 128 + (u % 32) * 4 + (u % 128) // 32
+    view[rows.to('cuda')] = xsf.to('cuda')
+
+
+@pytest.mark.parametrize('tokens', [1, 16, 64, 200])
+def test_fused_shared_expert_k128(single_rank_group, tokens):
+    """Routed experts plus one fused shared expert (two experts' worth of
+    intermediate) whose FP8 weights carry one UE8M0 scale per 128 x 128 block,
+    expanded to one packed row per output row before the transform."""
+    import gc_moe_b200 as G
+    e, h, i, k, s = 8, 1024, 512, 2, 2
+    case = LayerCase(single_rank_group, e, h, i, k, seed=6, num_shared_experts=s)
+    try:
+        g = torch.Generator().manual_seed(77)
+        sw1, sc1 = O.quantize_block_fp8(torch.randn((2 * s * i, h), generator=g) * 0.02)
+        sw2, sc2 = O.quantize_block_fp8(torch.randn((h, s * i), generator=g) * 0.02)
+        shared = {'w1': sw1, 'w1_codes': sc1, 'w2': sw2, 'w2_codes': sc2}
+        sl1, sl2 = G.transform_weights_for_gc_moe(
+            (sw1.cuda(), O.expand_block_sf_rows(sc1, 2 * s * i).cuda()),
+            (sw2.cuda(), O.expand_block_sf_rows(sc2, h).cuda()))
+        xq, xsf, idx, w = O.make_tokens(tokens, h, e, k, seed=60 + tokens)
+        bm = case.block_m(tokens)
+        case.stage(xq, xsf, idx, w)
+        _stage_shared_sf(case, xsf, tokens, bm)
+        y = torch.full((tokens, h), float('nan'), dtype=torch.bfloat16, device='cuda')
+        G.fp8_fp4_gc_moe(y, case.l1, case.l2, case.buf, sl1, sl2, activation_clamp=10.0,
+                         shared_recipe=(1, 128, 128))
+        torch.cuda.synchronize()
+        case.buf.raise_on_device_error()
+        ref = O.moe_layer([xq], [xsf], [idx], [w], case.q1, case.c1, case.q2, case.c2, [bm], clamp=10.0,
+                          shared=shared)
+        assert_close(y.cpu(), ref.y[0])
+        # the shared branch alone: routes all invalid -> y is the shared expert's output
+        idx[:] = -1
+        case.stage(xq, xsf, idx, w)
+        G.fp8_fp4_gc_moe(y, case.l1, case.l2, case.buf, sl1, sl2, activation_clamp=10.0,
+                         shared_recipe=(1, 128, 128))
+        torch.cuda.synchronize()
+        only = O.shared_expert(xq, xsf, shared, 10.0)
+        assert_close(y.cpu(), only)
+    finally:
+        case.close()
