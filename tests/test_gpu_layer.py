@@ -271,3 +271,30 @@ def test_fused_shared_expert_k128(single_rank_group, tokens):
         assert_close(y.cpu(), only)
     finally:
         case.close()
+
+
+def test_fused_shared_expert_k32(single_rank_group):
+    """Shared expert whose FP8 weights carry per-row K32 scales (shared recipe (1, 1, 32))."""
+    import gc_moe_b200 as G
+    e, h, i, k, s, tokens = 8, 1024, 512, 2, 1, 40
+    case = LayerCase(single_rank_group, e, h, i, k, seed=7, num_shared_experts=s)
+    try:
+        g = torch.Generator().manual_seed(78)
+        sw1, sf1 = O.quantize_act_fp8(torch.randn((2 * s * i, h), generator=g) * 0.02)
+        sw2, sf2 = O.quantize_act_fp8(torch.randn((h, s * i), generator=g) * 0.02)
+        shared = {'w1': sw1, 'w1_codes': O.sf_bytes(sf1), 'w2': sw2, 'w2_codes': O.sf_bytes(sf2), 'gran': 32}
+        mn = lambda t: t.t().contiguous().t()
+        sl1, sl2 = G.transform_weights_for_gc_moe((sw1.cuda(), mn(sf1).cuda()), (sw2.cuda(), mn(sf2).cuda()))
+        xq, xsf, idx, w = O.make_tokens(tokens, h, e, k, seed=90)
+        bm = case.block_m(tokens)
+        case.stage(xq, xsf, idx, w)
+        _stage_shared_sf(case, xsf, tokens, bm)
+        y = torch.full((tokens, h), float('nan'), dtype=torch.bfloat16, device='cuda')
+        G.fp8_fp4_gc_moe(y, case.l1, case.l2, case.buf, sl1, sl2, activation_clamp=10.0)
+        torch.cuda.synchronize()
+        case.buf.raise_on_device_error()
+        ref = O.moe_layer([xq], [xsf], [idx], [w], case.q1, case.c1, case.q2, case.c2, [bm], clamp=10.0,
+                          shared=shared)
+        assert_close(y.cpu(), ref.y[0])
+    finally:
+        case.close()
