@@ -36,6 +36,8 @@ struct CombineParams {
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineParams p) {
     const uint32_t vecs_per_token = p.hidden / 8;
     const uint64_t total = static_cast<uint64_t>(p.num_tokens) * vecs_per_token;
+    ptx::launch_dependents();
+    ptx::grid_dependency_wait();
     if (p.num_ranks > 1) {
         __shared__ uint32_t abort_word;
         if (threadIdx.x == 0) {
@@ -59,20 +61,41 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineP
 #pragma unroll
         for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
         const uint32_t nslots = p.topk + p.has_shared;
-        for (uint32_t g = 0; g < nslots; ++g) {
-            // order: shared slot (index k) first, then 0..k-1
-            const uint32_t slot = p.has_shared ? (g == 0 ? p.topk : g - 1) : g;
-            if (slot < p.topk) {
-                const unsigned long long e = static_cast<unsigned long long>(p.topk_idx[static_cast<size_t>(t) * p.topk + slot]);
-                if (e >= p.num_experts) continue;
-            }
-            const uint4 raw = *reinterpret_cast<const uint4*>(
-                p.slots + (static_cast<size_t>(slot) * p.capacity + t) * p.hidden + v * 8);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        // Slots are taken eight at a time: first every validity test, then every
+        // 16-byte load (independent, so their DRAM latencies overlap), then the
+        // additions in the fixed order.
+        for (uint32_t g0 = 0; g0 < nslots; g0 += 8) {
+            uint4 raw[8];
+            uint32_t valid = 0;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                acc[2 * c] = __fadd_rn(acc[2 * c], __uint_as_float(w[c] << 16));
-                acc[2 * c + 1] = __fadd_rn(acc[2 * c + 1], __uint_as_float(w[c] & 0xFFFF0000u));
+            for (uint32_t j = 0; j < 8; ++j) {
+                const uint32_t g = g0 + j;
+                if (g >= nslots) break;
+                // order: shared slot (index k) first, then 0..k-1
+                const uint32_t slot = p.has_shared ? (g == 0 ? p.topk : g - 1) : g;
+                bool ok = true;
+                if (slot < p.topk)
+                    ok = static_cast<unsigned long long>(p.topk_idx[static_cast<size_t>(t) * p.topk + slot]) < p.num_experts;
+                valid |= static_cast<uint32_t>(ok) << j;
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) {
+                const uint32_t g = g0 + j;
+                const uint32_t slot = p.has_shared ? (g == 0 ? p.topk : g - 1) : g;
+                raw[j] = make_uint4(0, 0, 0, 0);
+                if (valid >> j & 1u)
+                    raw[j] = *reinterpret_cast<const uint4*>(
+                        p.slots + (static_cast<size_t>(slot) * p.capacity + t) * p.hidden + v * 8);
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j) {
+                if (!(valid >> j & 1u)) continue;      // an invalid slot adds nothing (not even +0)
+                const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    acc[2 * c] = __fadd_rn(acc[2 * c], __uint_as_float(w[c] << 16));
+                    acc[2 * c + 1] = __fadd_rn(acc[2 * c + 1], __uint_as_float(w[c] & 0xFFFF0000u));
+                }
             }
         }
         uint4 out;

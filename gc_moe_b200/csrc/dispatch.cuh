@@ -89,6 +89,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     uint32_t* const slice_row = reinterpret_cast<uint32_t*>(slice_expert + slice);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+    ptx::launch_dependents();
     uint8_t* const my_arena = reinterpret_cast<uint8_t*>(p.arena_base[p.rank]);
     // Calls alternate between the two halves of every double-buffered counter;
     // the combine kernel bumps the call counter when a call retires, so replays

@@ -419,17 +419,47 @@ extern "C" int gcmoe_kernels_per_launch(const gcmoe_plan* plan) {
     return plan == nullptr ? 0 : 4;
 }
 
+// Launch with programmatic stream serialization: the kernel may start while
+// its predecessor in the stream is still running and orders itself with
+// griddepcontrol.wait, so its prologue overlaps the predecessor's tail.
+template <typename Params>
+static cudaError_t launch_dependent(void (*kernel)(Params), uint32_t grid, uint32_t block, uint32_t smem,
+                                    cudaStream_t stream, const Params& params, bool dependent) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
 extern "C" int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned mask, void* cuda_stream) {
     if (plan == nullptr) return fail(GCMOE_ERR_INVALID, "null plan");
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-    if (mask & 1u)
-        dispatch_kernel<<<plan->dispatch_grid, kDispatchThreads, plan->dispatch_smem, s>>>(plan->dispatch);
-    if (mask & 2u)
-        grouped_gemm_kernel<kPhaseL1><<<plan->gemm_grid_l1, kGemmThreads, plan->gemm_smem, s>>>(plan->l1);
-    if (mask & 4u)
-        grouped_gemm_kernel<kPhaseL2><<<plan->gemm_grid_l2, kGemmThreads, plan->gemm_smem, s>>>(plan->l2);
+    // Only a kernel launched together with its predecessor may overlap it.
+    bool chained = false;
+    if (mask & 1u) {
+        GCMOE_CUDA(launch_dependent(dispatch_kernel, plan->dispatch_grid, kDispatchThreads, plan->dispatch_smem, s,
+                                    plan->dispatch, false));
+        chained = true;
+    }
+    if (mask & 2u) {
+        GCMOE_CUDA(launch_dependent(grouped_gemm_kernel<kPhaseL1>, plan->gemm_grid_l1, kGemmThreads, plan->gemm_smem,
+                                    s, plan->l1, chained));
+        chained = true;
+    } else chained = false;
+    if (mask & 4u) {
+        GCMOE_CUDA(launch_dependent(grouped_gemm_kernel<kPhaseL2>, plan->gemm_grid_l2, kGemmThreads, plan->gemm_smem,
+                                    s, plan->l2, chained));
+        chained = true;
+    } else chained = false;
     if (mask & 8u)
-        combine_kernel<<<plan->combine_grid, kCombineThreads, 0, s>>>(plan->combine);
+        GCMOE_CUDA(launch_dependent(combine_kernel, plan->combine_grid, kCombineThreads, 0, s, plan->combine, chained));
     GCMOE_CUDA(cudaGetLastError());
     return GCMOE_OK;
 }

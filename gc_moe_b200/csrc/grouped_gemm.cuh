@@ -287,6 +287,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             ptx::prefetch_tensormap(&p.seg[g].tm_w);
         }
     }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), p.tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    // Everything above reads only kernel parameters; the tables below were
+    // written by the dispatch kernel (and the activations by the kernel before).
+    ptx::launch_dependents();
+    ptx::grid_dependency_wait();
     // Tables of both segments: [start (experts + 1) | count (experts)] each.
     const uint32_t experts0 = p.seg[0].experts;
     auto tbl_start = [&](uint32_t g) -> int* { return tables + (g ? 2 * experts0 + 1 : 0); };
@@ -295,10 +303,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t ne = p.seg[g].experts;
         for (uint32_t i = threadIdx.x; i <= ne; i += kGemmThreads) tbl_start(g)[i] = p.seg[g].tile_start[i];
         for (uint32_t i = threadIdx.x; i < ne; i += kGemmThreads) tbl_count(g)[i] = p.seg[g].count[i];
-    }
-    if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), p.tmem_cols);
-        ptx::tmem_relinquish();
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -343,7 +347,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const TileCoord tc = locate(tile);
             const GemmSegment& sg = p.seg[tc.seg];
             const uint32_t b = tc.block, nt = tc.n_tile, e = tc.expert;
-            const uint32_t sf_planes = (sg.k_blocks + sg.w_sf_kblocks - 1) / sg.w_sf_kblocks;
+            // w_sf_kblocks is 1 or 4: use mask and shift in the per-stage loop
+            const uint32_t kmask = sg.w_sf_kblocks - 1, kshift = sg.w_sf_kblocks == 4 ? 2u : 0u;
+            const uint32_t k_blocks = sg.k_blocks, w_tx = sg.weight_tx_bytes, w_sf_stride = sg.w_sf_stride;
+            const uint32_t act_sf_stride = sg.act_sf_stride;
+            const bool fp4 = sg.weight_format == 5u;
+            const uint32_t sf_planes = (k_blocks + kmask) >> kshift;
             const uint32_t* wsf = sg.w_sf + static_cast<size_t>(e) * sf_planes * sg.w_sf_stride + nt * kTileRows;
             const uint32_t* asf = sg.act_sf + static_cast<size_t>(b) * p.sf_block_m;
             if (kPhase != kPhaseL2 && !weights && p.num_ranks > 1 && !sg.shared && e != ready_expert) {
@@ -357,7 +366,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 ptx::fence_proxy_async_global();
                 ready_expert = e;
             }
-            for (uint32_t kb = 0; kb < sg.k_blocks; ++kb) {
+            for (uint32_t kb = 0; kb < k_blocks; ++kb) {
                 timer.start();
                 const bool got = mbar_wait(bar_empty + 8 * cur.stage, cur.phase ^ 1u, ctl, 1);
                 timer.stop_a();
@@ -368,9 +377,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 if (ptx::elect_one()) {
                     if (weights) {
                         // K128-granular scales: one packed word serves four K128 blocks
-                        const bool load_sf = kb % sg.w_sf_kblocks == 0;
-                        ptx::mbar_arrive_expect_tx(full, sg.weight_tx_bytes + (load_sf ? kWeightSfStageBytes : 0));
-                        if (sg.weight_format == 5u)
+                        const bool load_sf = (kb & kmask) == 0;
+                        ptx::mbar_arrive_expect_tx(full, w_tx + (load_sf ? kWeightSfStageBytes : 0));
+                        if (fp4)
                             ptx::tma_load_4d(base + L.w + cur.stage * kWeightStageBytes, &sg.tm_w, full, 0,
                                              nt * kTileRows, kb, e, ptx::kEvictFirst);
                         else
@@ -378,14 +387,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                              nt * kTileRows, kb, ptx::kEvictFirst);
                         if (load_sf)
                             ptx::bulk_load_1d(base + L.sfw + cur.stage * kWeightSfStageBytes,
-                                              wsf + static_cast<size_t>(kb / sg.w_sf_kblocks) * sg.w_sf_stride,
+                                              wsf + static_cast<size_t>(kb >> kshift) * w_sf_stride,
                                               kWeightSfStageBytes, full, ptx::kEvictFirst);
                     } else {
                         ptx::mbar_arrive_expect_tx(full, bm * kTileK + p.sf_block_m * 4);
                         ptx::tma_load_2d(base + L.a + cur.stage * bm * kTileK, &sg.tm_act, full, kb * kTileK,
                                          b * bm, ptx::kEvictLast);
                         ptx::bulk_load_1d(base + L.sfa + cur.stage * p.sf_block_m * 4,
-                                          asf + static_cast<size_t>(kb) * sg.act_sf_stride,
+                                          asf + static_cast<size_t>(kb) * act_sf_stride,
                                           p.sf_block_m * 4, full, ptx::kEvictLast);
                     }
                 }
@@ -420,6 +429,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 const GemmSegment& sg = p.seg[tc.seg];
                 const uint32_t n = round_up_u32(tc.valid, 16);
                 const uint32_t idesc = ptx::instr_desc(n, sg.weight_format);
+                const uint32_t kmask = sg.w_sf_kblocks - 1, k_blocks = sg.k_blocks;   // w_sf_kblocks is 1 or 4
                 const uint32_t as = p.acc_stages == 2 ? (it & 1u) : 0u;
                 const uint32_t acc_phase = p.acc_stages == 2 ? ((it >> 1) & 1u) : (it & 1u);
                 timer.start();
@@ -428,7 +438,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 if (!acc_free) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (as * 2 + m) * bm;
-                for (uint32_t kb = 0; kb < sg.k_blocks; ++kb) {
+                for (uint32_t kb = 0; kb < k_blocks; ++kb) {
                     timer.start();
                     const bool got = mbar_wait(bar_full + 8 * cur.stage, cur.phase, ctl, 3);
                     timer.stop_a();
@@ -439,26 +449,25 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         const uint32_t sfa_s = base + L.sfa + cur.stage * p.sf_block_m * 4;
                         // Weight scales of K128 granularity arrive with every fourth stage and
                         // stay in TMEM for the three stages that follow.
-                        if (kb % sg.w_sf_kblocks == 0)
+                        if ((kb & kmask) == 0)
                             ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
                         ptx::tmem_cp_sf(sfa_tmem, ptx::smem_desc(sfa_s, 128, false));
                         if (p.sf_block_m > 128)
                             ptx::tmem_cp_sf(sfa_tmem + 4, ptx::smem_desc(sfa_s + kSfChunkBytes, 128, false));
                         const uint64_t wdesc = ptx::smem_desc(base + L.w + cur.stage * kWeightStageBytes + m * kHalfStageBytes, 1024, true);
                         const uint64_t adesc = ptx::smem_desc(base + L.a + cur.stage * bm * kTileK, 1024, true);
-                        const uint32_t wide = sg.w_sf_kblocks == 4 ? (kb & 3u) : 0xFFu;
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k) {
                             // 32 K elements = 32 bytes in the swizzled row = +2 in 16-byte units.
                             // Scale byte: k-th byte of the stage's packed word (K32 scales), or
                             // byte kb % 4 of the four-stage word (K128 weight scales).
-                            const uint32_t w_byte = wide == 0xFFu ? k : wide;
+                            const uint32_t w_byte = kmask ? (kb & 3u) : k;
                             ptx::mma_mxf8f6f4(d_tmem, wdesc + 2 * k, adesc + 2 * k,
                                               idesc | (w_byte << 29) | (k << 4), sfw_tmem, sfa_tmem,
                                               (kb | k) != 0u ? 1u : 0u);
                         }
                         ptx::tc_commit(bar_empty + 8 * cur.stage);
-                        if (kb + 1 == sg.k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
+                        if (kb + 1 == k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
                     }
                     __syncwarp();
                     cur.advance(1, p.stages);

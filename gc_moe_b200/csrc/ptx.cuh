@@ -30,6 +30,18 @@ __device__ __forceinline__ long long clock_cycles() {
     return t;
 }
 
+// Programmatic dependent launch.  `grid_dependency_wait` returns once every
+// kernel this launch depends on has finished and its writes are visible;
+// before it a kernel may only do work that reads nothing those kernels wrote.
+// `launch_dependents` lets the next kernel of the stream start its own
+// prologue while this one is still running.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // True in exactly one lane of a converged warp.  Unlike `lane == 0`, the
 // compiler knows the guarded code runs in a single thread and can feed the
 // TMA / tcgen05 instructions from uniform registers directly.
