@@ -94,6 +94,29 @@ __device__ __forceinline__ bool flag_wait_eq(const uint32_t* flag, uint32_t expe
     }
 }
 
+// Wait until a counter written by other CTAs of this GPU reaches at least
+// `target` (acquire at GPU scope).
+__device__ __forceinline__ bool flag_wait_ge_gpu(const uint32_t* flag, uint32_t target,
+                                                 const WaitCtl& ctl, uint32_t site) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= target) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v >= target) return true;
+        if ((++spins & 15u) == 0u) {
+            if (*ctl.abort) return false;
+            if (ptx::globaltimer_ns() - t0 > ctl.timeout_ns) {
+                report_failure(ctl, kWaitTimeout, site, v, target);
+                return false;
+            }
+        }
+        __nanosleep(32);
+    }
+}
+
 // Per-call words the dispatch kernel leaves in plan-private scratch for the
 // kernels that follow it in the stream.
 enum CallInfoWord : int {

@@ -55,6 +55,8 @@ struct DispatchParams {
     int* expert_block_start;      // [E_loc + 1]
     uint32_t* call_info;          // [kCallInfoWords]
     int* shared_table;            // fused shared expert: {tokens, 0, row blocks}, or null
+    uint32_t* done_routed;        // per pool block: finished gate/up tiles, zeroed here for the GEMM launch
+    uint32_t* done_shared;        // same for the shared expert's row blocks, or null
     int* stats;                   // optional cumulative per-expert counter (may be null)
     uint32_t* status;
     uint64_t timeout_ns;
@@ -192,6 +194,13 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     }
     __syncthreads();
 
+    // Tile counters of this call's row blocks start from zero.
+    for (uint32_t i = blockIdx.x * kDispatchThreads + tid; i <= misc[1]; i += gridDim.x * kDispatchThreads)
+        p.done_routed[i] = 0;
+    if (p.done_shared != nullptr)
+        for (uint32_t i = blockIdx.x * kDispatchThreads + tid; i <= (p.num_tokens + p.block_m - 1) / p.block_m;
+             i += gridDim.x * kDispatchThreads)
+            p.done_shared[i] = 0;
     const uint32_t first_local = p.rank * EL;
     if (blockIdx.x == 0) {
         // ---- what this rank receives: the reference's count products and the

@@ -83,10 +83,10 @@ struct Plan {
     int num_sms = 0;
     uint32_t* status = nullptr;
     DispatchParams dispatch;
-    GemmParams l1, l2;
+    GemmParams up, down, fused;   // up tiles only, down tiles only, the layer's single GEMM launch
     CombineParams combine;
     uint32_t dispatch_grid = 1, dispatch_smem = 0;
-    uint32_t gemm_grid_l1 = 1, gemm_grid_l2 = 1, gemm_smem = 0;
+    uint32_t gemm_grid = 1, gemm_smem = 0;
     uint32_t combine_grid = 1;
 };
 
@@ -135,7 +135,9 @@ extern "C" const char* gcmoe_last_error(void) { return g_error; }
 extern "C" size_t gcmoe_scratch_bytes(const gcmoe_problem* problem) {
     if (problem == nullptr || problem->num_ranks <= 0) return 0;
     const size_t local = size_t(problem->num_experts / problem->num_ranks);
-    return round_up_u32(uint32_t(kStatusWords * 4 + (2 * local + 1) * 4 + kCallInfoWords * 4 + 3 * 4), 256);
+    const size_t bm = problem->block_m > 0 ? size_t(problem->block_m) : 16;
+    const size_t blocks = size_t(problem->ring_tokens) / bm + (size_t(problem->capacity) + bm - 1) / bm + 2;
+    return round_up_u32(uint32_t(kStatusWords * 4 + (2 * local + 1) * 4 + kCallInfoWords * 4 + 4 * 4 + blocks * 4), 256);
 }
 
 extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
@@ -175,9 +177,8 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
                         q.num_ranks, q.num_experts);
     }
 
-    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kPhaseL1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kPhaseL2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<kPhaseRaw>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     GCMOE_CUDA(cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
 
     gcmoe_plan* plan = new (std::nothrow) gcmoe_plan();
@@ -244,7 +245,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
 
     // ---- the two grouped GEMMs (each: shared-expert segment first, then routed)
     const uint32_t S = q.num_shared_experts, IS = S * I;
-    const uint32_t table_words = (2 * EL + 1) + (S ? 3 : 0);
+    const uint32_t table_words = 2 * ((2 * EL + 1) + (S ? 3 : 0));   // up and down segments each hold a copy
     const uint32_t stages = gemm_pick_stages(bm, sfbm, table_words);
     if (stages < 2) return bail(fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm));
     plan->gemm_smem = gemm_smem_layout(stages, bm, sfbm, table_words).total + 1024;
@@ -335,40 +336,59 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, weights, wdims, wstr, wbox, what);
     };
 
-    GemmParams& g1 = plan->l1;
-    GemmParams& g2 = plan->l2;
-    fill_common(g1);
-    fill_common(g2);
-    uint32_t nseg = 0;
+    // Per-row-block counters of finished up tiles (zeroed by the dispatch kernel).
+    uint32_t* done_routed = reinterpret_cast<uint32_t*>(shared_table + 4);
+    uint32_t* done_shared = done_routed + q.ring_tokens / bm + 1;
+    d.done_routed = done_routed;
+    d.done_shared = S ? done_shared : nullptr;
+
+    GemmSegment shared_up, shared_down, routed_up, routed_down;
+    memset(&shared_up, 0, sizeof(GemmSegment));
+    memset(&shared_down, 0, sizeof(GemmSegment));
+    memset(&routed_up, 0, sizeof(GemmSegment));
+    memset(&routed_down, 0, sizeof(GemmSegment));
     if (S) {
-        GemmSegment& s1 = g1.seg[0];
-        if (int rc = shared_segment(s1, arena + b.off_x, arena + b.off_shared_l1_acts_sf, H, b.sw1, b.sw1_sf,
+        if (int rc = shared_segment(shared_up, arena + b.off_x, arena + b.off_shared_l1_acts_sf, H, b.sw1, b.sw1_sf,
                                     b.sw1_sf_stride, 2 * IS, "shared gate/up GEMM")) return bail(rc);
-        s1.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_shared_l2_acts);
-        s1.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_shared_l2_acts_sf);
-        s1.out_sf_stride = uint32_t(b.shared_sf_rows);
-        s1.inter = IS;
-        GemmSegment& s2 = g2.seg[0];
-        if (int rc = shared_segment(s2, arena + b.off_shared_l2_acts, arena + b.off_shared_l2_acts_sf, IS, b.sw2,
-                                    b.sw2_sf, b.sw2_sf_stride, H, "shared down GEMM")) return bail(rc);
-        nseg = 1;
+        shared_up.kind = kSegUp;
+        shared_up.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_shared_l2_acts);
+        shared_up.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_shared_l2_acts_sf);
+        shared_up.out_sf_stride = uint32_t(b.shared_sf_rows);
+        shared_up.inter = IS;
+        shared_up.block_done = done_shared;
+        if (int rc = shared_segment(shared_down, arena + b.off_shared_l2_acts, arena + b.off_shared_l2_acts_sf, IS,
+                                    b.sw2, b.sw2_sf, b.sw2_sf_stride, H, "shared down GEMM")) return bail(rc);
+        shared_down.kind = kSegDown;
+        shared_down.block_done = done_shared;
+        shared_down.done_target = shared_up.n_tiles;
     }
-    {
-        GemmSegment& r1 = g1.seg[nseg];
-        if (int rc = routed_segment(r1, arena + b.off_l1_acts, arena + b.off_l1_acts_sf, H, b.w1, b.w1_sf,
-                                    b.w1_sf_stride, 2 * I, "gate/up GEMM")) return bail(rc);
-        r1.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts);
-        r1.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts_sf);
-        r1.out_sf_stride = q.sf_ring_tokens;
-        r1.inter = I;
-        r1.route_weight = reinterpret_cast<const float*>(arena + b.off_l1_topk_weights);
-        GemmSegment& r2 = g2.seg[nseg];
-        if (int rc = routed_segment(r2, arena + b.off_l2_acts, arena + b.off_l2_acts_sf, I, b.w2, b.w2_sf,
-                                    b.w2_sf_stride, H, "down GEMM")) return bail(rc);
-        r2.metadata = reinterpret_cast<const uint32_t*>(arena + b.off_metadata);
-        ++nseg;
-    }
-    g1.num_segments = g2.num_segments = nseg;
+    if (int rc = routed_segment(routed_up, arena + b.off_l1_acts, arena + b.off_l1_acts_sf, H, b.w1, b.w1_sf,
+                                b.w1_sf_stride, 2 * I, "gate/up GEMM")) return bail(rc);
+    routed_up.kind = kSegUp;
+    routed_up.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts);
+    routed_up.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts_sf);
+    routed_up.out_sf_stride = q.sf_ring_tokens;
+    routed_up.inter = I;
+    routed_up.route_weight = reinterpret_cast<const float*>(arena + b.off_l1_topk_weights);
+    routed_up.block_done = done_routed;
+    if (int rc = routed_segment(routed_down, arena + b.off_l2_acts, arena + b.off_l2_acts_sf, I, b.w2, b.w2_sf,
+                                b.w2_sf_stride, H, "down GEMM")) return bail(rc);
+    routed_down.kind = kSegDown;
+    routed_down.metadata = reinterpret_cast<const uint32_t*>(arena + b.off_metadata);
+    routed_down.block_done = done_routed;
+    routed_down.done_target = routed_up.n_tiles;
+
+    fill_common(plan->up);
+    fill_common(plan->down);
+    fill_common(plan->fused);
+    auto push = [](GemmParams& g, const GemmSegment& sg) { g.seg[g.num_segments++] = sg; };
+    if (S) { push(plan->up, shared_up); push(plan->fused, shared_up); }
+    push(plan->up, routed_up);
+    push(plan->fused, routed_up);
+    if (S) { push(plan->fused, shared_down); shared_down.done_target = 0; push(plan->down, shared_down); }
+    push(plan->fused, routed_down);
+    routed_down.done_target = 0;          // launched on its own, the up tiles finished in an earlier kernel
+    push(plan->down, routed_down);
     d.shared_table = S ? shared_table : nullptr;
 
     // Upper bound of pool blocks this call can produce: one partial block per
@@ -377,14 +397,12 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     uint64_t max_blocks = (all_routes < EL ? all_routes : EL) + all_routes / bm;
     if (max_blocks < 1) max_blocks = 1;
     const uint64_t shared_blocks = S ? (uint64_t(q.num_tokens) + bm - 1) / bm : 0;
-    auto grid_for = [&](const GemmParams& g) {
+    {
         // With several ranks the pool depends on what the other ranks send.
         const uint64_t tiles = P > 1 ? uint64_t(plan->num_sms)
-            : max_blocks * g.seg[g.num_segments - 1].n_tiles + (S ? shared_blocks * g.seg[0].n_tiles : 0);
-        return uint32_t(tiles < uint64_t(plan->num_sms) ? tiles : uint64_t(plan->num_sms));
-    };
-    plan->gemm_grid_l1 = grid_for(g1);
-    plan->gemm_grid_l2 = grid_for(g2);
+            : max_blocks * routed_up.n_tiles + (S ? shared_blocks * shared_up.n_tiles : 0);
+        plan->gemm_grid = uint32_t(tiles < uint64_t(plan->num_sms) ? tiles : uint64_t(plan->num_sms));
+    }
 
     // ---- combine
     CombineParams& c = plan->combine;
@@ -416,7 +434,7 @@ extern "C" int gcmoe_plan_destroy(gcmoe_plan* plan) {
 }
 
 extern "C" int gcmoe_kernels_per_launch(const gcmoe_plan* plan) {
-    return plan == nullptr ? 0 : 4;
+    return plan == nullptr ? 0 : 3;
 }
 
 // Launch with programmatic stream serialization: the kernel may start while
@@ -448,14 +466,11 @@ extern "C" int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned mask, void* cuda_
                                     plan->dispatch, false));
         chained = true;
     }
-    if (mask & 2u) {
-        GCMOE_CUDA(launch_dependent(grouped_gemm_kernel<kPhaseL1>, plan->gemm_grid_l1, kGemmThreads, plan->gemm_smem,
-                                    s, plan->l1, chained));
-        chained = true;
-    } else chained = false;
-    if (mask & 4u) {
-        GCMOE_CUDA(launch_dependent(grouped_gemm_kernel<kPhaseL2>, plan->gemm_grid_l2, kGemmThreads, plan->gemm_smem,
-                                    s, plan->l2, chained));
+    if (mask & 6u) {
+        // both GEMMs of the layer are one launch; either one alone is for tests and timing
+        const GemmParams& g = (mask & 6u) == 6u ? plan->fused : (mask & 2u) ? plan->up : plan->down;
+        GCMOE_CUDA(launch_dependent(grouped_gemm_kernel<false>, plan->gemm_grid, kGemmThreads, plan->gemm_smem, s, g,
+                                    chained));
         chained = true;
     } else chained = false;
     if (mask & 8u)
@@ -482,24 +497,23 @@ extern "C" int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* 
 }
 
 extern "C" int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cuda_stream) {
-    if (plan == nullptr || out == 0 || which < 0 || which > 1) return fail(GCMOE_ERR_INVALID, "bad argument");
-    GemmParams g = which == 0 ? plan->l1 : plan->l2;
+    if (plan == nullptr || out == 0 || which < 0 || which > 2) return fail(GCMOE_ERR_INVALID, "bad argument");
+    GemmParams g = which == 0 ? plan->up : which == 1 ? plan->down : plan->fused;
     g.timing = reinterpret_cast<unsigned long long*>(out);
-    const uint32_t grid = which == 0 ? plan->gemm_grid_l1 : plan->gemm_grid_l2;
+    const uint32_t grid = plan->gemm_grid;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-    if (which == 0)
-        grouped_gemm_kernel<kPhaseL1><<<grid, kGemmThreads, plan->gemm_smem, s>>>(g);
-    else
-        grouped_gemm_kernel<kPhaseL2><<<grid, kGemmThreads, plan->gemm_smem, s>>>(g);
+    grouped_gemm_kernel<false><<<grid, kGemmThreads, plan->gemm_smem, s>>>(g);
     GCMOE_CUDA(cudaGetLastError());
     return int(grid);
 }
 
 extern "C" int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream) {
     if (plan == nullptr || out == 0) return fail(GCMOE_ERR_INVALID, "null argument");
-    GemmParams g = plan->l1;
+    GemmParams g = plan->up;
+    g.seg[0] = plan->up.seg[plan->up.num_segments - 1];   // the routed gate/up segment alone
+    g.num_segments = 1;
     g.raw_out = reinterpret_cast<float*>(out);
-    grouped_gemm_kernel<kPhaseRaw><<<plan->gemm_grid_l1, kGemmThreads, plan->gemm_smem,
+    grouped_gemm_kernel<true><<<plan->gemm_grid, kGemmThreads, plan->gemm_smem,
                                     static_cast<cudaStream_t>(cuda_stream)>>>(g);
     GCMOE_CUDA(cudaGetLastError());
     return GCMOE_OK;
@@ -519,8 +533,8 @@ extern "C" int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cud
 namespace gcmoe {
 
 constexpr int kStaticMaxLocalExperts = 128;
-constexpr size_t kStaticScratchBytes = 1280;   // status + counts + prefix for 128 local experts, 256-aligned
-static_assert(kStaticScratchBytes >= kStatusWords * 4 + (2 * kStaticMaxLocalExperts + 1) * 4 + kCallInfoWords * 4 + 12, "static scratch too small");
+constexpr size_t kStaticScratchBytes = 65536;  // status, counts, prefix for 128 local experts, tile counters of ~16000 row blocks
+static_assert(kStaticScratchBytes >= kStatusWords * 4 + (2 * kStaticMaxLocalExperts + 1) * 4 + kCallInfoWords * 4 + 16, "static scratch too small");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 

@@ -53,13 +53,24 @@ constexpr int kMaxStages = 16;
 constexpr int kMaxBlockM = 240;
 constexpr int kSmemLimit = 232448;         // opt-in dynamic shared memory per CTA on sm_100
 
-enum GemmPhase : int { kPhaseL1 = 0, kPhaseL2 = 1, kPhaseRaw = 2 };
+// What a segment's tiles compute after the K loop.
+enum SegmentKind : uint32_t {
+    kSegUp = 0,     // gate/up projection: SwiGLU, route weight, FP8 requantisation -> intermediate
+    kSegDown = 1    // down projection: BF16 rows scattered to the source rank's combine slots
+};
+constexpr int kMaxSegments = 4;   // shared up, routed up, shared down, routed down
 
-// One grouped problem of a launch: the routed experts of this rank, or the
-// fused shared expert (one "expert" whose rows are this rank's own tokens,
-// FP8 weights).  A launch runs the shared segment's tiles first -- they depend
-// on nothing another GPU sends, so they hide the dispatch exchange -- and the
-// routed segment's after them.
+// One grouped problem of a launch: the up or the down projection of the routed
+// experts of this rank, or of the fused shared expert (one "expert" whose rows
+// are this rank's own tokens, FP8 weights).  One launch runs all of them as one
+// work list -- shared up, routed up, shared down, routed down -- so that a CTA
+// that runs out of up tiles continues with down tiles instead of idling at a
+// kernel boundary.  The shared tiles come first because they depend on nothing
+// another GPU sends and so hide the dispatch exchange.  A down tile needs every
+// up tile of its row block: up epilogues count finished tiles per row block in
+// `block_done` and the down tile's activation producer waits for the count.
+// All up tiles precede all down tiles in every CTA's order and every CTA of the
+// grid is resident (grid <= SMs, one CTA per SM), so the wait cannot deadlock.
 struct GemmSegment {
     CUtensorMap tm_act;     // u8 [rows][K], box 128 x BM, 128-byte swizzle
     CUtensorMap tm_w;       // FP4: 16U4_ALIGN16B [E][K/128][rows][128], box 128 x 256
@@ -78,18 +89,21 @@ struct GemmSegment {
     uint32_t weight_format;  // 5 = e2m1 (FP4), 0 = e4m3
     uint32_t weight_tx_bytes;  // bytes the weight tile's TMA reports to the stage barrier
     uint32_t shared;         // rows are own tokens: no route weight, no arrival wait, output slot = topk
-    // ---- gate/up epilogue (kPhaseL1)
+    uint32_t kind;           // SegmentKind
+    uint32_t* block_done;    // [row blocks] up: tiles finished; down: what to wait for
+    uint32_t done_target;    // down: up tiles per row block (0 = do not wait)
+    // ---- gate/up epilogue
     uint8_t* out_acts;        // e4m3 [rows][I]
     uint8_t* out_sf;          // bytes of the MN-major packed scale ring
     const float* route_weight;  // [rows], unused for the shared segment
     uint32_t out_sf_stride;   // words between K128 planes of out_sf
     uint32_t inter;           // row length of out_acts
-    // ---- down epilogue (kPhaseL2)
+    // ---- down epilogue
     const uint32_t* metadata;  // (src_rank, src_token, slot) per pool row, unused for the shared segment
 };
 
 struct GemmParams {
-    GemmSegment seg[2];
+    GemmSegment seg[kMaxSegments];
     uint32_t num_segments;
     uint32_t* status;
     uint64_t timeout_ns;
@@ -108,7 +122,7 @@ struct GemmParams {
     uint32_t hidden;
     uint32_t topk;
     uint32_t rank;
-    // ---- raw epilogue (kPhaseRaw): FP32 accumulators of segment 0, [rows][w_rows]
+    // ---- raw epilogue (test hook): FP32 accumulators of segment 0, [rows][w_rows]
     float* raw_out;
     // ---- multi-rank: arrival counters of the dispatched rows (gate/up) and of
     // the combine contributions (down); unused on a single rank
@@ -158,7 +172,7 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
     // full[stages], empty[stages], acc_full[2], acc_empty[2], drain[2], then the
     // TMEM base slot and the abort word
     l.tables = l.bars + (2 * stages + 6) * 8 + 16;
-    l.amax = l.tables + round_up_u32(table_words * 4, 16);
+    l.amax = l.tables + round_up_u32((table_words + 16) * 4, 16);   // tables + per-segment offsets and tile prefix
     l.rows = l.amax + 2 * 4 * 16 * 4;                 // amax exchange [2][4][16] floats
     l.out = round_up_u32(l.rows + 2 * block_m * 16, 16);   // per-block row info, double buffered
     l.total = l.out + 2 * 16 * kHalfRows * 2;          // output transpose: [2][16 tokens][128 channels] bf16
@@ -240,7 +254,7 @@ struct TileCoord {
     uint32_t seg, block, n_tile, expert, valid;
 };
 
-template <int kPhase>
+template <bool kRaw>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -268,7 +282,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     ctl.status = p.status;
     ctl.abort = abort_word;
     ctl.timeout_ns = p.timeout_ns;
-    ctl.kernel = kPhase == kPhaseL2 ? kKernelGemmL2 : kKernelGemmL1;
+    ctl.kernel = kKernelGemmL1;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
@@ -295,45 +309,64 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     // written by the dispatch kernel (and the activations by the kernel before).
     ptx::launch_dependents();
     ptx::grid_dependency_wait();
-    // Tables of both segments: [start (experts + 1) | count (experts)] each.
-    const uint32_t experts0 = p.seg[0].experts;
-    auto tbl_start = [&](uint32_t g) -> int* { return tables + (g ? 2 * experts0 + 1 : 0); };
-    auto tbl_count = [&](uint32_t g) -> int* { return tbl_start(g) + p.seg[g].experts + 1; };
+    // Tables of every segment: [start (experts + 1) | count (experts)] each, then
+    // per segment the table offset and the prefix of tile counts.
+    uint32_t* const seg_meta = reinterpret_cast<uint32_t*>(tables + p.table_words);   // [4] offsets, [5] tile prefix
+    if (threadIdx.x == 0) {
+        uint32_t off = 0;
+        for (uint32_t g = 0; g < p.num_segments; ++g) {
+            seg_meta[g] = off;
+            off += 2 * p.seg[g].experts + 1;
+        }
+    }
+    __syncthreads();
     for (uint32_t g = 0; g < p.num_segments; ++g) {
         const uint32_t ne = p.seg[g].experts;
-        for (uint32_t i = threadIdx.x; i <= ne; i += kGemmThreads) tbl_start(g)[i] = p.seg[g].tile_start[i];
-        for (uint32_t i = threadIdx.x; i < ne; i += kGemmThreads) tbl_count(g)[i] = p.seg[g].count[i];
+        int* const start = tables + seg_meta[g];
+        for (uint32_t i = threadIdx.x; i <= ne; i += kGemmThreads) start[i] = p.seg[g].tile_start[i];
+        for (uint32_t i = threadIdx.x; i < ne; i += kGemmThreads) start[ne + 1 + i] = p.seg[g].count[i];
     }
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (uint32_t g = 0; g < p.num_segments; ++g) {
+            seg_meta[4 + g] = run;
+            run += static_cast<uint32_t>(tables[seg_meta[g] + p.seg[g].experts]) * p.seg[g].n_tiles;
+        }
+        for (uint32_t g = p.num_segments; g <= kMaxSegments; ++g) seg_meta[4 + g] = run;
+    }
+    __syncthreads();
     const uint32_t tmem_base = *tmem_slot;
 
     const uint32_t bm = p.block_m;
-    const uint32_t tiles0 = static_cast<uint32_t>(tbl_start(0)[p.seg[0].experts]) * p.seg[0].n_tiles;
-    const uint32_t tiles1 = p.num_segments > 1
-        ? static_cast<uint32_t>(tbl_start(1)[p.seg[1].experts]) * p.seg[1].n_tiles : 0u;
-    const uint32_t total_tiles = tiles0 + tiles1;
+    const uint32_t total_tiles = seg_meta[4 + kMaxSegments];
 
     // Decode a tile index: segment, row block, 256-row weight slice, owning
     // expert (last e with start[e] <= block) and the block's valid rows.
     auto locate = [&](uint32_t tile) -> TileCoord {
         TileCoord c;
-        c.seg = tile >= tiles0 ? 1u : 0u;
-        const uint32_t local = tile - (c.seg ? tiles0 : 0u);
-        const uint32_t nt = p.seg[c.seg].n_tiles;
+        c.seg = 0;
+#pragma unroll
+        for (uint32_t g = 1; g < kMaxSegments; ++g) c.seg += tile >= seg_meta[4 + g] ? 1u : 0u;
+        const uint32_t local = tile - seg_meta[4 + c.seg];
+        const uint32_t nt = p.seg[c.seg].n_tiles, ne = p.seg[c.seg].experts;
         c.block = local / nt;
         c.n_tile = local - c.block * nt;
-        const int* const start = tbl_start(c.seg);
-        uint32_t lo = 0, hi = p.seg[c.seg].experts;   // start[lo] <= block < start[hi]
+        const int* const start = tables + seg_meta[c.seg];
+        uint32_t lo = 0, hi = ne;   // start[lo] <= block < start[hi]
         while (hi - lo > 1) {
             const uint32_t mid = (lo + hi) >> 1;
             if (static_cast<uint32_t>(start[mid]) <= c.block) lo = mid; else hi = mid;
         }
         c.expert = lo;
-        const uint32_t left = static_cast<uint32_t>(tbl_count(c.seg)[lo]) - (c.block - static_cast<uint32_t>(start[lo])) * bm;
+        const uint32_t left = static_cast<uint32_t>(start[ne + 1 + lo]) - (c.block - static_cast<uint32_t>(start[lo])) * bm;
         c.valid = left < bm ? left : bm;
         return c;
+    };
+    auto rows_of_expert = [&](uint32_t seg, uint32_t e) -> uint32_t {
+        return static_cast<uint32_t>(tables[seg_meta[seg] + p.seg[seg].experts + 1 + e]);
     };
 
     if (warp == 0 || warp == 2) {
@@ -355,16 +388,24 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t sf_planes = (k_blocks + kmask) >> kshift;
             const uint32_t* wsf = sg.w_sf + static_cast<size_t>(e) * sf_planes * sg.w_sf_stride + nt * kTileRows;
             const uint32_t* asf = sg.act_sf + static_cast<size_t>(b) * p.sf_block_m;
-            if (kPhase != kPhaseL2 && !weights && p.num_ranks > 1 && !sg.shared && e != ready_expert) {
+            if (!weights && sg.kind == kSegUp && p.num_ranks > 1 && !sg.shared && e != ready_expert) {
                 // The rows of this expert are pushed by other GPUs: wait until all of
                 // them have landed, then order the TMA (async proxy) after the acquire.
                 uint32_t landed = 1;
                 if (lane == 0)
                     landed = flag_wait_eq(p.rows_arrived + p.call_info[kCallGeneration] * kMaxLocalExperts + e,
-                                          static_cast<uint32_t>(tbl_count(tc.seg)[e]), ctl, 5);
+                                          rows_of_expert(tc.seg, e), ctl, 5);
                 if (!__shfl_sync(0xffffffffu, landed, 0)) { ok = false; break; }
                 ptx::fence_proxy_async_global();
                 ready_expert = e;
+            }
+            if (!weights && sg.kind == kSegDown && sg.done_target != 0) {
+                // The block's intermediate rows are written by the up tiles of this same
+                // launch, possibly on other SMs: wait for all of them.
+                uint32_t done = 1;
+                if (lane == 0) done = flag_wait_ge_gpu(sg.block_done + b, sg.done_target, ctl, 7);
+                if (!__shfl_sync(0xffffffffu, done, 0)) { ok = false; break; }
+                ptx::fence_proxy_async_global();
             }
             for (uint32_t kb = 0; kb < k_blocks; ++kb) {
                 timer.start();
@@ -503,19 +544,20 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // Stage what the stores need to know about the block's rows while the
             // main loop is still running: route weight (gate/up) or destination.
             uint32_t* const info = row_info + (it & 1u) * bm * 4;
-            if (kPhase == kPhaseL1 && p.num_ranks > 1 && !sg.shared) {
+            if (!kRaw && sg.kind == kSegUp && p.num_ranks > 1 && !sg.shared) {
                 // Route weights are pushed by other GPUs together with the rows.
                 bool landed = true;
                 if (etid == 0)
                     landed = flag_wait_eq(p.rows_arrived + p.call_info[kCallGeneration] * kMaxLocalExperts + e,
-                                          static_cast<uint32_t>(tbl_count(tc.seg)[e]), ctl, 6);
+                                          rows_of_expert(tc.seg, e), ctl, 6);
                 if (!all_epilogue_threads(landed)) { ok = false; break; }
             }
-            if constexpr (kPhase == kPhaseL1) {
+            if (kRaw) {
+            } else if (sg.kind == kSegUp) {
                 // the shared expert's rows carry no route weight
                 for (uint32_t i = etid; i < valid; i += 128)
                     info[i] = sg.shared ? __float_as_uint(1.0f) : __float_as_uint(sg.route_weight[row0 + i]);
-            } else if constexpr (kPhase == kPhaseL2) {
+            } else {
                 if (sg.shared) {
                     // own tokens: row t goes to this rank's combine slot `topk`
                     for (uint32_t i = etid; i < valid; i += 128) {
@@ -550,7 +592,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(bar_acc_empty + 8 * as);
                 }
-                if constexpr (kPhase == kPhaseRaw) {
+                if constexpr (kRaw) {
 #pragma unroll
                     for (uint32_t c = 0; c < 16; ++c) {
                         const uint32_t col = c0 + c;
@@ -558,7 +600,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                             p.raw_out[static_cast<size_t>(row0 + col) * sg.w_rows + nh * kHalfRows + r] =
                                 __uint_as_float(vi[c]);
                     }
-                } else if constexpr (kPhase == kPhaseL2) {
+                } else if (sg.kind == kSegDown) {
                     // Transpose through shared memory so that a token's 128 channels leave
                     // as 16-byte vectors: 256 contiguous bytes per half-warp, which is what
                     // NVLink (and HBM) want, instead of 2-byte elements per lane.
@@ -631,7 +673,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     xbuf ^= 1u;
                 }
             }
-            if (kPhase == kPhaseL2 && p.num_ranks > 1 && !sg.shared) {
+            if (!kRaw && sg.kind == kSegUp) {
+                // Publish the tile: make the intermediate rows visible to the TMA reads of
+                // the down tiles (other SMs), then count it for its row block.
+                ptx::fence_proxy_async_global();
+                epilogue_barrier();
+                if (etid == 0) {
+                    __threadfence();
+                    atomicAdd(sg.block_done + b, 1u);
+                }
+            }
+            if (!kRaw && sg.kind == kSegDown && p.num_ranks > 1 && !sg.shared) {
                 // Tell each source rank how many of its rows this tile has written
                 // (rows of one source are contiguous in a block).  The barrier orders
                 // every epilogue thread's stores before the leader's release.

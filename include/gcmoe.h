@@ -99,7 +99,8 @@ int gcmoe_version(void);
 const char* gcmoe_last_error(void);
 
 /* Bytes of plan-private device scratch a plan for `problem` needs (status
- * block, per-expert counts, pool-block prefix, call info).  The caller allocates and
+ * block, per-expert counts, pool-block prefix, call info, per-block tile
+ * counters).  The caller allocates and
  * zero-fills it once. */
 size_t gcmoe_scratch_bytes(const gcmoe_problem* problem);
 
@@ -112,15 +113,16 @@ int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffers* buffers
                       gcmoe_plan** plan);
 int gcmoe_plan_destroy(gcmoe_plan* plan);
 
-/* Enqueue one layer call (dispatch, gate/up GEMM, down GEMM, combine) on
+/* Enqueue one layer call (dispatch, the expert GEMMs, combine) on
  * `cuda_stream` (a cudaStream_t).  Plain stream launches: a caller that is
  * capturing the stream into a CUDA graph captures the layer.  Replaces
  * GreenContextPair.launch (gc_moe/runtime/gc_moe.py:369-418). */
 int gcmoe_launch(gcmoe_plan* plan, void* cuda_stream);
 
 /* Enqueue only the kernels selected by `kernel_mask` (bit 0 dispatch, bit 1
- * gate/up GEMM, bit 2 down GEMM, bit 3 combine); used by the parity tests and
- * for per-kernel timing. */
+ * gate/up tiles, bit 2 down tiles, bit 3 combine); bits 1 and 2 together are
+ * the layer's single GEMM launch, either alone runs only those tiles.  Used by
+ * the parity tests and for per-kernel timing. */
 int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned kernel_mask, void* cuda_stream);
 
 /* Number of kernels gcmoe_launch enqueues per call. */
@@ -137,7 +139,8 @@ int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* words);
  * descriptor and scale plumbing. */
 int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream);
 
-/* Run one of the two grouped GEMMs (which = 0 gate/up, 1 down) with per-role
+/* Run the grouped GEMM launch (which = 0 gate/up tiles only, 1 down tiles only,
+ * 2 both as in a layer call) with per-role
  * cycle counters written to `out`: uint64 [grid][5 roles][4] = {cycles in the
  * role loop, cycles in its first wait, cycles in its second wait, tiles};
  * roles: weight producer, activation producer, MMA warp 0, MMA warp 1,
@@ -151,9 +154,10 @@ int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cud
  * loop whose pool was sized at start-up, or code running where cudaMalloc
  * would synchronise or is forbidden -- which therefore cannot hand over the
  * scratch block gcmoe_plan_create asks for.  The kernels' scratch (status
- * words, per-expert token counts, pool-block prefix) lives in a fixed
- * 1280-byte device array inside the library instead, enough for 128 local
- * experts; more local experts are rejected with GCMOE_ERR_UNSUPPORTED.
+ * words, per-expert token counts, pool-block prefix, per-block tile counters)
+ * lives in a fixed 64 KiB device array inside the library instead, enough for
+ * 128 local experts and about 16000 row blocks; larger problems are rejected
+ * with GCMOE_ERR_UNSUPPORTED.
  * `buffers->scratch` is ignored; the arena, weights and y are still the
  * caller's.  No cudaMalloc / cudaFree or any other allocating device routine
  * is called; one small host object lives for the duration of the call.
