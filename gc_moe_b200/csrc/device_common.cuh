@@ -142,6 +142,13 @@ __host__ __device__ __forceinline__ uint32_t bytes(uint32_t ranks, uint32_t expe
 }
 }  // namespace exchange
 
+// Rows (tokens) per GEMM tile for a pool laid out in blocks of `block_m`: small
+// blocks are grouped up to 64 tokens because a tcgen05.mma costs the same issue
+// time for 16 columns as for 64; from 64 up the tiles are the pool blocks.
+__host__ __device__ __forceinline__ uint32_t gemm_tile_rows(uint32_t block_m) {
+    return block_m < 64u ? 64u : block_m;
+}
+
 __host__ __device__ __forceinline__ uint32_t round_up_u32(uint32_t v, uint32_t m) {
     return (v + m - 1) / m * m;
 }

@@ -52,7 +52,9 @@ struct DispatchParams {
     uint64_t off_exchange;
     // plan-private outputs
     int* expert_count;            // [E_loc]
-    int* expert_block_start;      // [E_loc + 1]
+    int* expert_block_start;      // [E_loc + 1] pool-block prefix (reference layout)
+    int* expert_tile_start;       // [E_loc + 1] prefix of the GEMM tiles per expert
+    int* expert_row_start;        // [E_loc] first pool row per expert
     uint32_t* call_info;          // [kCallInfoWords]
     int* shared_table;            // fused shared expert: {tokens, 0, row blocks}, or null
     uint32_t* done_routed;        // per pool block: finished gate/up tiles, zeroed here for the GEMM launch
@@ -63,14 +65,16 @@ struct DispatchParams {
     uint32_t num_ranks, rank, num_experts, local_experts;
     uint32_t num_tokens, topk, hidden, capacity;
     uint32_t block_m, sf_ring;    // sf_ring: words between K128 planes of l1_acts_sf
+    uint32_t private_sf_row;      // row offset, in each scale plane, of the tile-ordered scale copy (0 = none)
 };
 
-// Dynamic shared memory: five u32 per expert (own count, own routes before the
-// slice, total over sources, routes of lower sources, first pool block), one
-// block-M per rank, then the CTA's slice: expert id and pool row per route.
+// Dynamic shared memory: six u32 per expert (own count, own routes before the
+// slice, total over sources, routes of lower sources, first pool block, first
+// GEMM tile), one block-M per rank, then the CTA's slice: expert id, pool row and
+// position inside the expert per route.
 __host__ __device__ inline uint32_t dispatch_smem_bytes(uint32_t num_experts, uint32_t num_ranks,
                                                         uint32_t slice) {
-    return (5 * num_experts + num_ranks + 8 + 2 * slice) * 4;
+    return (6 * num_experts + num_ranks + 8 + 3 * slice) * 4;
 }
 
 __global__ void __launch_bounds__(kDispatchThreads)
@@ -85,10 +89,12 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     uint32_t* const total = before + E;         // [E] routes of all ranks
     uint32_t* const lower = total + E;          // [E] routes of source ranks below this one
     uint32_t* const first_block = lower + E;    // [E] first pool block of the expert at its owner
-    uint32_t* const bm_of = first_block + E;    // [P] block-M of each rank's pool
+    uint32_t* const first_tile = first_block + E;   // [E] first GEMM tile of the expert at its owner
+    uint32_t* const bm_of = first_tile + E;     // [P] block-M of each rank's pool
     uint32_t* const misc = bm_of + P;           // [8] abort word, own pool blocks, own valid routes
     int* const slice_expert = reinterpret_cast<int*>(misc + 8);
     uint32_t* const slice_row = reinterpret_cast<uint32_t*>(slice_expert + slice);
+    uint32_t* const slice_pos = slice_row + slice;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     ptx::launch_dependents();
@@ -162,29 +168,39 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     }
     __syncthreads();
 
-    // Pool-block prefix of every owner's local experts (warp w: owners w, w+8, ...).
+    // Pool-block prefix and GEMM-tile prefix of every owner's local experts
+    // (warp w: owners w, w+8, ...).  The GEMMs tile an expert's rows by
+    // gemm_tile_rows(BM) tokens, which is more than BM for small BM, so that an
+    // expert with many rows costs fewer passes over its weights.
     for (uint32_t r = warp; r < P; r += kDispatchThreads / 32) {
         const uint32_t bm = bm_of[r], base = r * EL;
+        const uint32_t tn = p.private_sf_row ? gemm_tile_rows(bm) : bm;
         const uint32_t per_lane = (EL + 31) / 32;
-        uint32_t sum = 0;
+        uint32_t sum = 0, tsum = 0;
         for (uint32_t i = 0; i < per_lane; ++i) {
             const uint32_t l = lane * per_lane + i;
-            if (l < EL) sum += (total[base + l] + bm - 1) / bm;
+            if (l < EL) {
+                sum += (total[base + l] + bm - 1) / bm;
+                tsum += (total[base + l] + tn - 1) / tn;
+            }
         }
-        uint32_t incl = sum;
+        uint32_t incl = sum, tincl = tsum;
         for (uint32_t d = 1; d < 32; d <<= 1) {
             const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += v;
+            const uint32_t tv = __shfl_up_sync(0xffffffffu, tincl, d);
+            if (lane >= d) { incl += v; tincl += tv; }
         }
-        uint32_t run = incl - sum;
+        uint32_t run = incl - sum, trun = tincl - tsum;
         for (uint32_t i = 0; i < per_lane; ++i) {
             const uint32_t l = lane * per_lane + i;
             if (l < EL) {
                 first_block[base + l] = run;
+                first_tile[base + l] = trun;
                 run += (total[base + l] + bm - 1) / bm;
+                trun += (total[base + l] + tn - 1) / tn;
             }
         }
-        if (r == p.rank && lane == 31) misc[1] = incl;      // pool blocks of this rank
+        if (r == p.rank && lane == 31) { misc[1] = incl; misc[3] = tincl; }   // pool blocks, GEMM tiles of this rank
     }
     if (blockIdx.x == 0) {
         uint32_t mine = 0;
@@ -195,7 +211,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     __syncthreads();
 
     // Tile counters of this call's row blocks start from zero.
-    for (uint32_t i = blockIdx.x * kDispatchThreads + tid; i <= misc[1]; i += gridDim.x * kDispatchThreads)
+    for (uint32_t i = blockIdx.x * kDispatchThreads + tid; i <= misc[3]; i += gridDim.x * kDispatchThreads)
         p.done_routed[i] = 0;
     if (p.done_shared != nullptr)
         for (uint32_t i = blockIdx.x * kDispatchThreads + tid; i <= (p.num_tokens + p.block_m - 1) / p.block_m;
@@ -215,6 +231,8 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             const uint32_t n = total[first_local + l];
             p.expert_count[l] = static_cast<int>(n);
             p.expert_block_start[l] = static_cast<int>(first_block[first_local + l]);
+            p.expert_tile_start[l] = static_cast<int>(first_tile[first_local + l]);
+            p.expert_row_start[l] = static_cast<int>(first_block[first_local + l] * p.block_m);
             for (uint32_t s = 0; s < P; ++s)
                 recv[static_cast<size_t>(s) * EL + l] = P > 1 ? counts[static_cast<size_t>(s) * E + first_local + l] : n;
             // high word: number of source ranks that have reported
@@ -232,6 +250,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         }
         if (tid == 0) {
             p.expert_block_start[EL] = static_cast<int>(misc[1]);
+            p.expert_tile_start[EL] = static_cast<int>(misc[3]);
             *reinterpret_cast<uint32_t*>(my_arena + p.off_routed_pool_blocks) = misc[1];
             p.call_info[kCallGeneration] = gen;
             p.call_info[kCallCombineRows] = misc[2];
@@ -240,6 +259,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
                 p.shared_table[0] = static_cast<int>(p.num_tokens);
                 p.shared_table[1] = 0;
                 p.shared_table[2] = static_cast<int>((p.num_tokens + p.block_m - 1) / p.block_m);
+                p.shared_table[3] = 0;     // the shared expert's rows start at token 0
             }
         }
     }
@@ -270,6 +290,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             reinterpret_cast<float*>(dst_arena + p.off_l1_weights)[row] = p.topk_weights[a];
         }
         slice_row[a - lo] = row;
+        slice_pos[a - lo] = row == 0xFFFFFFFFu ? 0u : row - first_block[e >= 0 ? e : 0] * bm_of[(e >= 0 ? e : 0) / EL];
     }
     __syncthreads();
 
@@ -292,8 +313,16 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         const uint32_t block = row / bm, u = row - block * bm;
         const uint32_t sf_row = block * sf_block + sf_row_in_block(u);
         uint32_t* sf_dst = reinterpret_cast<uint32_t*>(dst_arena + p.off_l1_acts_sf);
-        for (uint32_t w = lane; w < sf_words; w += 32)
-            sf_dst[static_cast<size_t>(w) * p.sf_ring + sf_row] = p.x_sf[static_cast<size_t>(t) * sf_words + w];
+        // second copy, ordered by GEMM tile, when the tiles are not the pool blocks
+        const uint32_t tn = p.private_sf_row ? gemm_tile_rows(bm) : bm;
+        const uint32_t pos = slice_pos[a - lo];
+        const uint32_t tile_row = p.private_sf_row + (first_tile[e] + pos / tn) * round_up_u32(tn, 128) +
+                                  sf_row_in_block(pos % tn);
+        for (uint32_t w = lane; w < sf_words; w += 32) {
+            const uint32_t word = p.x_sf[static_cast<size_t>(t) * sf_words + w];
+            sf_dst[static_cast<size_t>(w) * p.sf_ring + sf_row] = word;
+            if (tn != bm) sf_dst[static_cast<size_t>(w) * p.sf_ring + tile_row] = word;
+        }
         if (P > 1) {
             __syncwarp();
             if (lane == 0) {

@@ -135,9 +135,9 @@ extern "C" const char* gcmoe_last_error(void) { return g_error; }
 extern "C" size_t gcmoe_scratch_bytes(const gcmoe_problem* problem) {
     if (problem == nullptr || problem->num_ranks <= 0) return 0;
     const size_t local = size_t(problem->num_experts / problem->num_ranks);
-    const size_t bm = problem->block_m > 0 ? size_t(problem->block_m) : 16;
-    const size_t blocks = size_t(problem->ring_tokens) / bm + (size_t(problem->capacity) + bm - 1) / bm + 2;
-    return round_up_u32(uint32_t(kStatusWords * 4 + (2 * local + 1) * 4 + kCallInfoWords * 4 + 4 * 4 + blocks * 4), 256);
+    // status | count | block prefix | tile prefix | row start | call info | shared table | tile counters
+    const size_t counters = size_t(problem->ring_tokens) / 16 + local + size_t(problem->capacity) / 16 + 4;
+    return round_up_u32(uint32_t(kStatusWords * 4 + (4 * local + 2) * 4 + kCallInfoWords * 4 + 4 * 4 + counters * 4), 256);
 }
 
 extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
@@ -205,7 +205,18 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     plan->status = reinterpret_cast<uint32_t*>(b.scratch);
     int* expert_count = reinterpret_cast<int*>(b.scratch + kStatusWords * 4);
     int* expert_block_start = expert_count + EL;
-    uint32_t* call_info = reinterpret_cast<uint32_t*>(expert_block_start + EL + 1);
+    int* expert_tile_start = expert_block_start + EL + 1;
+    int* expert_row_start = expert_tile_start + EL + 1;
+    uint32_t* call_info = reinterpret_cast<uint32_t*>(expert_row_start + EL);
+
+    // GEMM tiles of small block-M pools span several pool blocks (gemm_tile_rows); their
+    // scale words are then kept a second time, in tile order, in the upper half of every
+    // plane of the scale rings, which the reference layout never touches for block-M >= 16.
+    // Every rank must take the same decision: it depends on the buffer geometry only.
+    const uint32_t private_sf_row =
+        (uint64_t(q.ring_tokens) / 64 + EL + 1) * 128 <= uint64_t(q.sf_ring_tokens) / 2 ? uint32_t(q.sf_ring_tokens) / 2 : 0u;
+    const uint32_t tn = private_sf_row ? gemm_tile_rows(bm) : bm;     // rows per GEMM tile on this rank
+    const uint32_t sftn = round_up_u32(tn, 128);
 
     // ---- dispatch
     DispatchParams& d = plan->dispatch;
@@ -228,6 +239,9 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     d.call_info = call_info;
     d.expert_count = expert_count;
     d.expert_block_start = expert_block_start;
+    d.expert_tile_start = expert_tile_start;
+    d.expert_row_start = expert_row_start;
+    d.private_sf_row = private_sf_row;
     d.stats = reinterpret_cast<int*>(b.stats);
     d.status = plan->status;
     d.timeout_ns = timeout_ns;
@@ -245,25 +259,25 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
 
     // ---- the two grouped GEMMs (each: shared-expert segment first, then routed)
     const uint32_t S = q.num_shared_experts, IS = S * I;
-    const uint32_t table_words = 2 * ((2 * EL + 1) + (S ? 3 : 0));   // up and down segments each hold a copy
-    const uint32_t stages = gemm_pick_stages(bm, sfbm, table_words);
+    const uint32_t table_words = 2 * ((3 * EL + 1) + (S ? 4 : 0));   // up and down segments each hold a copy
+    const uint32_t stages = gemm_pick_stages(tn, sftn, table_words);
     if (stages < 2) return bail(fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm));
-    plan->gemm_smem = gemm_smem_layout(stages, bm, sfbm, table_words).total + 1024;
+    plan->gemm_smem = gemm_smem_layout(stages, tn, sftn, table_words).total + 1024;
     // Two accumulator stages (epilogue overlaps the next tile) while they fit TMEM.
-    const uint32_t acc_stages = gemm_tmem_columns(bm, sfbm, 2) <= 512 ? 2u : 1u;
-    if (gemm_tmem_columns(bm, sfbm, acc_stages) > 512)
+    const uint32_t acc_stages = gemm_tmem_columns(tn, sftn, 2) <= 512 ? 2u : 1u;
+    if (gemm_tmem_columns(tn, sftn, acc_stages) > 512)
         return bail(fail(GCMOE_ERR_UNSUPPORTED, "TMEM budget exceeded"));
 
     auto fill_common = [&](GemmParams& g) {
         memset(&g, 0, sizeof(g));
         g.status = plan->status;
         g.timeout_ns = timeout_ns;
-        g.block_m = bm;
-        g.sf_block_m = sfbm;
+        g.block_m = tn;
+        g.sf_block_m = sftn;
         g.stages = stages;
         g.acc_stages = acc_stages;
         g.table_words = table_words;
-        g.tmem_cols = pow2_at_least(gemm_tmem_columns(bm, sfbm, acc_stages));
+        g.tmem_cols = pow2_at_least(gemm_tmem_columns(tn, sftn, acc_stages));
         g.clamp = q.clamp;
         g.has_clamp = q.has_clamp != 0;
         g.fast_math = q.fast_math != 0;
@@ -282,23 +296,32 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     // Routed experts: FP4 weights [EL][K/128][rows][64 B], pool rows as activations.
     auto routed_segment = [&](GemmSegment& sg, uint64_t acts, uint64_t acts_sf, uint32_t k, uint64_t weights,
                               uint64_t w_sf, uint64_t w_sf_stride, uint32_t w_rows, const char* what) -> int {
-        sg.tile_start = expert_block_start;
+        sg.tile_start = expert_tile_start;
         sg.count = expert_count;
+        sg.row_start = expert_row_start;
         sg.experts = EL;
+        sg.tile_rows = tn;
+        sg.narrow_rows = bm;          // tn == bm: both maps are the same box
+        sg.sf_chunk_rows = sftn;
+        sg.ref_block_m = bm;
+        sg.out_sf_private = tn != bm ? private_sf_row : 0u;
         sg.w_rows = w_rows;
         sg.k_blocks = k / 128;
         sg.n_tiles = w_rows / kTileRows;
         sg.weight_format = 5;
         sg.weight_tx_bytes = kTileRows * 128 / 2;
         sg.w_sf_kblocks = 1;
-        sg.act_sf = reinterpret_cast<const uint32_t*>(acts_sf);
+        // tiles that are not pool blocks read the tile-ordered scale copy
+        sg.act_sf = reinterpret_cast<const uint32_t*>(acts_sf) + (tn != bm ? private_sf_row : 0u);
         sg.act_sf_stride = q.sf_ring_tokens;
         sg.w_sf = reinterpret_cast<const uint32_t*>(w_sf);
         sg.w_sf_stride = uint32_t(w_sf_stride);
         const uint64_t adims[2] = {k, uint64_t(q.ring_tokens)};
         const uint64_t astr[1] = {k};
-        const uint32_t abox[2] = {128, bm};
+        const uint32_t abox[2] = {128, tn}, nbox[2] = {128, bm};
         if (int rc = encode_map(&sg.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
+            return rc;
+        if (int rc = encode_map(&sg.tm_act_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, nbox, what))
             return rc;
         // 128-element (64-byte) rows of one K128 tile are adjacent, so a 128 x 256
         // box is one contiguous 16 KiB range in HBM.
@@ -314,7 +337,12 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         sg.shared = 1;
         sg.count = shared_table;
         sg.tile_start = shared_table + 1;
+        sg.row_start = shared_table + 3;
         sg.experts = 1;
+        sg.tile_rows = bm;            // the caller stages the scales in block-M order
+        sg.narrow_rows = bm;
+        sg.sf_chunk_rows = sfbm;
+        sg.ref_block_m = bm;
         sg.w_rows = w_rows;
         sg.k_blocks = k / 128;
         sg.n_tiles = w_rows / kTileRows;
@@ -330,6 +358,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         const uint32_t abox[2] = {128, bm};
         if (int rc = encode_map(&sg.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
             return rc;
+        sg.tm_act_narrow = sg.tm_act;
         const uint64_t wdims[3] = {128, w_rows, k / 128};
         const uint64_t wstr[2] = {128, uint64_t(w_rows) * 128};
         const uint32_t wbox[3] = {128, kTileRows, 1};
@@ -338,7 +367,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
 
     // Per-row-block counters of finished up tiles (zeroed by the dispatch kernel).
     uint32_t* done_routed = reinterpret_cast<uint32_t*>(shared_table + 4);
-    uint32_t* done_shared = done_routed + q.ring_tokens / bm + 1;
+    uint32_t* done_shared = done_routed + q.ring_tokens / 16 + EL + 1;
     d.done_routed = done_routed;
     d.done_shared = S ? done_shared : nullptr;
 
@@ -534,7 +563,7 @@ namespace gcmoe {
 
 constexpr int kStaticMaxLocalExperts = 128;
 constexpr size_t kStaticScratchBytes = 65536;  // status, counts, prefix for 128 local experts, tile counters of ~16000 row blocks
-static_assert(kStaticScratchBytes >= kStatusWords * 4 + (2 * kStaticMaxLocalExperts + 1) * 4 + kCallInfoWords * 4 + 16, "static scratch too small");
+static_assert(kStaticScratchBytes >= kStatusWords * 4 + (4 * kStaticMaxLocalExperts + 2) * 4 + kCallInfoWords * 4 + 16, "static scratch too small");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 

@@ -72,13 +72,18 @@ constexpr int kMaxSegments = 4;   // shared up, routed up, shared down, routed d
 // All up tiles precede all down tiles in every CTA's order and every CTA of the
 // grid is resident (grid <= SMs, one CTA per SM), so the wait cannot deadlock.
 struct GemmSegment {
-    CUtensorMap tm_act;     // u8 [rows][K], box 128 x BM, 128-byte swizzle
+    CUtensorMap tm_act;     // u8 [rows][K], box 128 x tile_rows, 128-byte swizzle
+    CUtensorMap tm_act_narrow;  // same tensor, box 128 x narrow_rows: tiles with few valid rows
     CUtensorMap tm_w;       // FP4: 16U4_ALIGN16B [E][K/128][rows][128], box 128 x 256
                             // FP8: u8 [K/128][rows][128], box 128 x 256
     const uint32_t* act_sf;  // packed scale words, MN-major: word (kb, r) at kb * act_sf_stride + r
     const uint32_t* w_sf;    // word (e, plane, row) at (e * planes + plane) * w_sf_stride + row
-    const int* tile_start;   // [experts + 1] prefix of the experts' row blocks
+    const int* tile_start;   // [experts + 1] prefix of the experts' tile counts (ceil(rows / tile_rows))
     const int* count;        // [experts] rows per expert
+    const int* row_start;    // [experts] first row of the expert in the activation tensor
+    uint32_t tile_rows;      // rows (tokens) per tile = MMA N upper bound; independent of the pool's block-M
+    uint32_t narrow_rows;    // box height of tm_act_narrow
+    uint32_t sf_chunk_rows;  // scale rows per tile in act_sf: tile_rows rounded up to 128
     uint32_t act_sf_stride;  // words between consecutive K128 planes of act_sf
     uint32_t w_sf_stride;    // words between consecutive planes of w_sf
     uint32_t w_sf_kblocks;   // K128 blocks one w_sf word covers: 1 (K32 scales) or 4 (K128 scales)
@@ -97,6 +102,9 @@ struct GemmSegment {
     uint8_t* out_sf;          // bytes of the MN-major packed scale ring
     const float* route_weight;  // [rows], unused for the shared segment
     uint32_t out_sf_stride;   // words between K128 planes of out_sf
+    uint32_t ref_block_m;     // block-M of the pool layout: where out_sf rows go in the reference layout
+    uint32_t out_sf_private;  // row offset, inside each plane, of the tile-ordered copy the down tiles
+                              // read (0 = tiles coincide with pool blocks, no second copy)
     uint32_t inter;           // row length of out_acts
     // ---- down epilogue
     const uint32_t* metadata;  // (src_rank, src_token, slot) per pool row, unused for the shared segment
@@ -107,8 +115,8 @@ struct GemmParams {
     uint32_t num_segments;
     uint32_t* status;
     uint64_t timeout_ns;
-    uint32_t block_m;        // BM
-    uint32_t sf_block_m;     // BM rounded up to 128 (scale rows reserved per row block)
+    uint32_t block_m;        // largest tile_rows of the launch: rows of an activation stage, accumulator stride
+    uint32_t sf_block_m;     // that, rounded up to 128: scale rows of an activation stage
     uint32_t stages;
     uint32_t acc_stages;     // 2, or 1 when two accumulator stages exceed TMEM
     uint32_t table_words;    // shared-memory words for the segments' tables
@@ -251,7 +259,7 @@ struct StageCursor {
 // Where a tile of the launch's work list lives: which segment, which row block
 // of which expert, which 256-row slice of the expert's weights.
 struct TileCoord {
-    uint32_t seg, block, n_tile, expert, valid;
+    uint32_t seg, block, n_tile, expert, valid, row0;   // block: tile index inside the segment
 };
 
 template <bool kRaw>
@@ -298,6 +306,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         ptx::fence_mbar_init();
         for (uint32_t g = 0; g < p.num_segments; ++g) {
             ptx::prefetch_tensormap(&p.seg[g].tm_act);
+            ptx::prefetch_tensormap(&p.seg[g].tm_act_narrow);
             ptx::prefetch_tensormap(&p.seg[g].tm_w);
         }
     }
@@ -316,7 +325,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         uint32_t off = 0;
         for (uint32_t g = 0; g < p.num_segments; ++g) {
             seg_meta[g] = off;
-            off += 2 * p.seg[g].experts + 1;
+            off += 3 * p.seg[g].experts + 1;
         }
     }
     __syncthreads();
@@ -324,7 +333,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const uint32_t ne = p.seg[g].experts;
         int* const start = tables + seg_meta[g];
         for (uint32_t i = threadIdx.x; i <= ne; i += kGemmThreads) start[i] = p.seg[g].tile_start[i];
-        for (uint32_t i = threadIdx.x; i < ne; i += kGemmThreads) start[ne + 1 + i] = p.seg[g].count[i];
+        for (uint32_t i = threadIdx.x; i < ne; i += kGemmThreads) {
+            start[ne + 1 + i] = p.seg[g].count[i];
+            start[2 * ne + 1 + i] = p.seg[g].row_start[i];
+        }
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -361,8 +373,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             if (static_cast<uint32_t>(start[mid]) <= c.block) lo = mid; else hi = mid;
         }
         c.expert = lo;
-        const uint32_t left = static_cast<uint32_t>(start[ne + 1 + lo]) - (c.block - static_cast<uint32_t>(start[lo])) * bm;
-        c.valid = left < bm ? left : bm;
+        const uint32_t tn = p.seg[c.seg].tile_rows, t = c.block - static_cast<uint32_t>(start[lo]);
+        const uint32_t left = static_cast<uint32_t>(start[ne + 1 + lo]) - t * tn;
+        c.valid = left < tn ? left : tn;
+        c.row0 = static_cast<uint32_t>(start[2 * ne + 1 + lo]) + t * tn;
         return c;
     };
     auto rows_of_expert = [&](uint32_t seg, uint32_t e) -> uint32_t {
@@ -387,7 +401,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const bool fp4 = sg.weight_format == 5u;
             const uint32_t sf_planes = (k_blocks + kmask) >> kshift;
             const uint32_t* wsf = sg.w_sf + static_cast<size_t>(e) * sf_planes * sg.w_sf_stride + nt * kTileRows;
-            const uint32_t* asf = sg.act_sf + static_cast<size_t>(b) * p.sf_block_m;
+            const uint32_t sf_chunk = sg.sf_chunk_rows;
+            const uint32_t* asf = sg.act_sf + static_cast<size_t>(b) * sf_chunk;
+            // few valid rows: fetch a narrow box instead of the whole tile height
+            const bool narrow = tc.valid <= sg.narrow_rows;
+            const uint32_t act_rows = narrow ? sg.narrow_rows : sg.tile_rows;
+            const CUtensorMap* const act_map = narrow ? &sg.tm_act_narrow : &sg.tm_act;
             if (!weights && sg.kind == kSegUp && p.num_ranks > 1 && !sg.shared && e != ready_expert) {
                 // The rows of this expert are pushed by other GPUs: wait until all of
                 // them have landed, then order the TMA (async proxy) after the acquire.
@@ -431,12 +450,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                               wsf + static_cast<size_t>(kb >> kshift) * w_sf_stride,
                                               kWeightSfStageBytes, full, ptx::kEvictFirst);
                     } else {
-                        ptx::mbar_arrive_expect_tx(full, bm * kTileK + p.sf_block_m * 4);
-                        ptx::tma_load_2d(base + L.a + cur.stage * bm * kTileK, &sg.tm_act, full, kb * kTileK,
-                                         b * bm, ptx::kEvictLast);
+                        ptx::mbar_arrive_expect_tx(full, act_rows * kTileK + sf_chunk * 4);
+                        ptx::tma_load_2d(base + L.a + cur.stage * bm * kTileK, act_map, full, kb * kTileK,
+                                         tc.row0, ptx::kEvictLast);
                         ptx::bulk_load_1d(base + L.sfa + cur.stage * p.sf_block_m * 4,
                                           asf + static_cast<size_t>(kb) * act_sf_stride,
-                                          p.sf_block_m * 4, full, ptx::kEvictLast);
+                                          sf_chunk * 4, full, ptx::kEvictLast);
                     }
                 }
                 __syncwarp();
@@ -493,7 +512,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         if ((kb & kmask) == 0)
                             ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
                         ptx::tmem_cp_sf(sfa_tmem, ptx::smem_desc(sfa_s, 128, false));
-                        if (p.sf_block_m > 128)
+                        if (sg.sf_chunk_rows > 128)
                             ptx::tmem_cp_sf(sfa_tmem + 4, ptx::smem_desc(sfa_s + kSfChunkBytes, 128, false));
                         const uint64_t wdesc = ptx::smem_desc(base + L.w + cur.stage * kWeightStageBytes + m * kHalfStageBytes, 1024, true);
                         const uint64_t adesc = ptx::smem_desc(base + L.a + cur.stage * bm * kTileK, 1024, true);
@@ -540,7 +559,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t ncols = round_up_u32(valid, 16);
             const uint32_t as = p.acc_stages == 2 ? (it & 1u) : 0u;
             const uint32_t acc_phase = p.acc_stages == 2 ? ((it >> 1) & 1u) : (it & 1u);
-            const uint32_t row0 = b * bm;       // pool row of accumulator column 0
+            const uint32_t row0 = tc.row0;      // activation row of accumulator column 0
             // Stage what the stores need to know about the block's rows while the
             // main loop is still running: route weight (gate/up) or destination.
             uint32_t* const info = row_info + (it & 1u) * bm * 4;
@@ -627,7 +646,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     // same channels, so lane l and lane l^8 hold a channel's pair.  The
                     // gate lane finishes the even columns, the up lane the odd ones.
                     const uint32_t is_up = (r >> 3) & 1u;
-                    const uint32_t ch = nh * 64 + (r >> 4) * 8 + (r & 7u);   // intermediate channel
                     float res[8], amax[8];
 #pragma unroll
                     for (uint32_t j = 0; j < 8; ++j) {
@@ -653,20 +671,42 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         for (uint32_t j = 0; j < 8; ++j) mine[2 * j + is_up] = amax[j];
                     }
                     epilogue_barrier();
+                    // Quantise into a [16 tokens][64 channels] byte tile in shared memory, then
+                    // store it as 16-byte vectors (64 contiguous bytes per token) and let one
+                    // thread per (token, 32-channel group) write the scale byte.
+                    uint8_t* const otile = reinterpret_cast<uint8_t*>(out_stage) + xbuf * 4096;
+                    const uint32_t c64 = (r >> 4) * 8 + (r & 7u);        // channel inside this half's 64
 #pragma unroll
                     for (uint32_t j = 0; j < 8; ++j) {
-                        const uint32_t col = c0 + 2 * j + is_up;
-                        const float mx = fmaxf(amax[j], other[2 * j + is_up]);
+                        const uint32_t col16 = 2 * j + is_up;
+                        const float mx = fmaxf(amax[j], other[col16]);
                         const uint32_t code = ue8m0_scale_byte(mx);
                         const float inv = __uint_as_float((254u - code) << 23);
-                        const uint32_t byte = ptx::cvt_e4m3x2(__fmul_rn(res[j], inv), 0.0f) & 0xFFu;
+                        otile[col16 * 64 + c64] = static_cast<uint8_t>(ptx::cvt_e4m3x2(__fmul_rn(res[j], inv), 0.0f) & 0xFFu);
+                        if ((q & 1u) == 0u && (lane & 0x17u) == 0u) otile[1024 + col16 * 2 + (q >> 1)] = static_cast<uint8_t>(code);
+                    }
+                    epilogue_barrier();
+                    if (etid < 64) {
+                        const uint32_t col16 = etid >> 2, seg16 = etid & 3u, col = c0 + col16;
+                        if (col < valid)
+                            *reinterpret_cast<uint4*>(sg.out_acts + static_cast<size_t>(row0 + col) * sg.inter + nh * 64 + seg16 * 16) =
+                                *reinterpret_cast<const uint4*>(otile + col16 * 64 + seg16 * 16);
+                    } else if (etid < 96) {
+                        const uint32_t col16 = (etid - 64) >> 1, grp = etid & 1u, col = c0 + col16;
                         if (col < valid) {
-                            sg.out_acts[static_cast<size_t>(row0 + col) * sg.inter + ch] = static_cast<uint8_t>(byte);
-                            if ((q & 1u) == 0u && (lane & 0x17u) == 0u) {
-                                const uint32_t k32 = nh * 2 + (q >> 1);   // index of the 32-channel group
-                                const size_t word = static_cast<size_t>(k32 >> 2) * sg.out_sf_stride +
-                                                    static_cast<size_t>(b) * p.sf_block_m + sf_row_in_block(col);
-                                sg.out_sf[word * 4 + (k32 & 3u)] = static_cast<uint8_t>(code);
+                            const uint8_t code = otile[1024 + col16 * 2 + grp];
+                            const uint32_t k32 = nh * 2 + grp;           // index of the 32-channel group
+                            // reference layout: position of the pool row inside its block-M block
+                            const uint32_t row = row0 + col, rb = row / sg.ref_block_m;
+                            const size_t plane = static_cast<size_t>(k32 >> 2) * sg.out_sf_stride;
+                            const size_t word = plane + static_cast<size_t>(rb) * round_up_u32(sg.ref_block_m, 128) +
+                                                sf_row_in_block(row - rb * sg.ref_block_m);
+                            sg.out_sf[word * 4 + (k32 & 3u)] = code;
+                            if (sg.out_sf_private != 0u) {
+                                // tile-ordered copy for the down tiles of this launch
+                                const size_t mine = plane + sg.out_sf_private +
+                                                    static_cast<size_t>(b) * sg.sf_chunk_rows + sf_row_in_block(col);
+                                sg.out_sf[mine * 4 + (k32 & 3u)] = code;
                             }
                         }
                     }
