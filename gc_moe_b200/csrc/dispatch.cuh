@@ -37,7 +37,7 @@
 
 namespace gcmoe {
 
-constexpr int kDispatchThreads = 256;
+constexpr int kDispatchThreads = 512;
 
 struct DispatchParams {
     // this rank's staged inputs (arena views)
@@ -136,7 +136,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
                 reinterpret_cast<uint32_t*>(ex + exchange::kSourceBlockM)[gen * kMaxRanks + p.rank] = p.block_m;
             __syncthreads();
             if (tid == 0) {
-                ptx::fence_acq_rel_sys();
+                // the release is cumulative over the CTA's stores ordered before it by the barrier
                 ptx::st_release_sys(reinterpret_cast<uint32_t*>(ex + exchange::kCountsReady) + gen * kMaxRanks + p.rank,
                                     epoch + 1u);
             }
@@ -308,8 +308,17 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         const uint32_t t = a / p.topk;
         const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(t) * p.hidden);
         uint4* dst = reinterpret_cast<uint4*>(dst_arena + p.off_l1_acts + static_cast<size_t>(row) * p.hidden);
-#pragma unroll 4
-        for (uint32_t v = lane; v < row_vecs; v += 32) dst[v] = src[v];
+        // eight 16-byte loads in flight per lane before the first store: one memory
+        // latency per 4 KiB of row instead of one per 512 bytes
+        for (uint32_t v0 = lane; v0 < row_vecs; v0 += 256) {
+            uint4 part[8];
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j)
+                if (v0 + j * 32 < row_vecs) part[j] = src[v0 + j * 32];
+#pragma unroll
+            for (uint32_t j = 0; j < 8; ++j)
+                if (v0 + j * 32 < row_vecs) dst[v0 + j * 32] = part[j];
+        }
         const uint32_t block = row / bm, u = row - block * bm;
         const uint32_t sf_row = block * sf_block + sf_row_in_block(u);
         uint32_t* sf_dst = reinterpret_cast<uint32_t*>(dst_arena + p.off_l1_acts_sf);
@@ -325,11 +334,9 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         }
         if (P > 1) {
             __syncwarp();
-            if (lane == 0) {
-                ptx::fence_acq_rel_sys();
+            if (lane == 0)      // release, cumulative over the warp's stores ordered by __syncwarp
                 ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(dst_arena + p.off_exchange + exchange::kRowsArrived) +
                                              gen * kMaxLocalExperts + (e - owner * EL), 1u);
-            }
         }
     }
 }

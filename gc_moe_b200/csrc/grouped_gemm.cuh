@@ -729,7 +729,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 // every epilogue thread's stores before the leader's release.
                 epilogue_barrier();
                 if (etid == 0) {
-                    ptx::fence_acq_rel_sys();
                     const uint32_t gen = p.call_info[kCallGeneration];
                     uint32_t run_rank = info[0], run = 0;
                     for (uint32_t i = 0; i <= valid; ++i) {
