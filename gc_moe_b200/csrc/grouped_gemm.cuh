@@ -480,6 +480,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t sf_cols = 4 + p.sf_block_m / 32;
             const uint32_t sfw_tmem = tmem_base + p.acc_stages * 2 * bm + m * sf_cols;   // 4 columns
             const uint32_t sfa_tmem = sfw_tmem + 4;                            // sf_block_m / 32 columns
+            const uint64_t wdesc0 = ptx::smem_desc(base + L.w + m * kHalfStageBytes, 1024, true);
+            const uint64_t adesc0 = ptx::smem_desc(base + L.a, 1024, true);
+            const uint64_t sfw_desc0 = ptx::smem_desc(base + L.sfw + m * kSfChunkBytes, 128, false);
+            const uint64_t sfa_desc0 = ptx::smem_desc(base + L.sfa, 128, false);
             StageCursor cur;
             uint32_t it = 0;
             bool ok = true;
@@ -490,6 +494,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 const uint32_t n = round_up_u32(tc.valid, 16);
                 const uint32_t idesc = ptx::instr_desc(n, sg.weight_format);
                 const uint32_t kmask = sg.w_sf_kblocks - 1, k_blocks = sg.k_blocks;   // w_sf_kblocks is 1 or 4
+                const bool wide_sf = sg.sf_chunk_rows > 128;
                 const uint32_t as = p.acc_stages == 2 ? (it & 1u) : 0u;
                 const uint32_t acc_phase = p.acc_stages == 2 ? ((it >> 1) & 1u) : (it & 1u);
                 timer.start();
@@ -505,27 +510,22 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     if (!got) { ok = false; break; }
                     ptx::tc_fence_after();
                     if (ptx::elect_one()) {
-                        const uint32_t sfw_s = base + L.sfw + cur.stage * kWeightSfStageBytes + m * kSfChunkBytes;
-                        const uint32_t sfa_s = base + L.sfa + cur.stage * p.sf_block_m * 4;
+                        // Descriptors of this stage: the per-warp base plus the stage's offset in
+                        // 16-byte units (all shared-memory addresses fit the 14-bit field).
+                        const uint64_t sfw_desc = sfw_desc0 + cur.stage * (kWeightSfStageBytes >> 4);
+                        const uint64_t sfa_desc = sfa_desc0 + cur.stage * (p.sf_block_m >> 2);
                         // Weight scales of K128 granularity arrive with every fourth stage and
                         // stay in TMEM for the three stages that follow.
-                        if ((kb & kmask) == 0)
-                            ptx::tmem_cp_sf(sfw_tmem, ptx::smem_desc(sfw_s, 128, false));
-                        ptx::tmem_cp_sf(sfa_tmem, ptx::smem_desc(sfa_s, 128, false));
-                        if (sg.sf_chunk_rows > 128)
-                            ptx::tmem_cp_sf(sfa_tmem + 4, ptx::smem_desc(sfa_s + kSfChunkBytes, 128, false));
-                        const uint64_t wdesc = ptx::smem_desc(base + L.w + cur.stage * kWeightStageBytes + m * kHalfStageBytes, 1024, true);
-                        const uint64_t adesc = ptx::smem_desc(base + L.a + cur.stage * bm * kTileK, 1024, true);
-#pragma unroll
-                        for (uint32_t k = 0; k < 4; ++k) {
-                            // 32 K elements = 32 bytes in the swizzled row = +2 in 16-byte units.
-                            // Scale byte: k-th byte of the stage's packed word (K32 scales), or
-                            // byte kb % 4 of the four-stage word (K128 weight scales).
-                            const uint32_t w_byte = kmask ? (kb & 3u) : k;
-                            ptx::mma_mxf8f6f4(d_tmem, wdesc + 2 * k, adesc + 2 * k,
-                                              idesc | (w_byte << 29) | (k << 4), sfw_tmem, sfa_tmem,
-                                              (kb | k) != 0u ? 1u : 0u);
-                        }
+                        if ((kb & kmask) == 0) ptx::tmem_cp_sf(sfw_tmem, sfw_desc);
+                        ptx::tmem_cp_sf(sfa_tmem, sfa_desc);
+                        if (wide_sf) ptx::tmem_cp_sf(sfa_tmem + 4, sfa_desc + (kSfChunkBytes >> 4));
+                        // Scale byte of MMA k: k-th byte of the stage's packed words (K32 scales);
+                        // for K128 weight scales the weight byte is kb % 4 for all four.
+                        const uint32_t first = kmask ? (idesc | ((kb & 3u) << 29)) : idesc;
+                        ptx::mma_mxf8f6f4_k128(d_tmem, wdesc0 + cur.stage * (kWeightStageBytes >> 4),
+                                               adesc0 + cur.stage * (bm * kTileK >> 4), first,
+                                               kmask ? (1u << 4) : ((1u << 29) | (1u << 4)), sfw_tmem, sfa_tmem,
+                                               kb != 0u ? 1u : 0u);
                         ptx::tc_commit(bar_empty + 8 * cur.stage);
                         if (kb + 1 == k_blocks) ptx::tc_commit(bar_acc_full + 8 * as);
                     }

@@ -168,6 +168,29 @@ __device__ __forceinline__ void mma_mxf8f6f4(uint32_t d_tmem, uint64_t a_desc, u
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
         : "memory");
 }
+// The four K32 MMAs of one K128 stage in one block.  Both descriptors advance by
+// 32 bytes (+2 in 16-byte units) per step and the instruction descriptor by
+// `idesc_step` (the scale-byte selectors); the first MMA overwrites the
+// accumulator when `accumulate_first` is 0.
+__device__ __forceinline__ void mma_mxf8f6f4_k128(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                  uint32_t idesc, uint32_t idesc_step, uint32_t sfa_tmem,
+                                                  uint32_t sfb_tmem, uint32_t accumulate_first) {
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 da, db; .reg .b32 id;\n"
+        "mov.b64 da, %1; mov.b64 db, %2; mov.b32 id, %3;\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, id, [%6], [%7], p;\n"
+        "add.u64 da, da, 2; add.u64 db, db, 2; add.u32 id, id, %4;\n"
+        "setp.ne.b32 p, 1, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, id, [%6], [%7], p;\n"
+        "add.u64 da, da, 2; add.u64 db, db, 2; add.u32 id, id, %4;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, id, [%6], [%7], p;\n"
+        "add.u64 da, da, 2; add.u64 db, db, 2; add.u32 id, id, %4;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], da, db, id, [%6], [%7], p;\n"
+        "}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(idesc_step), "r"(accumulate_first), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
 // 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated to the
 // four 32-lane quarters (the layout block-scale factors are read from).
 __device__ __forceinline__ void tmem_cp_sf(uint32_t tmem_col, uint64_t smem_desc) {
