@@ -152,6 +152,45 @@ def main():
         except RuntimeError as exc:
             failures.append(f'replay: {exc}')
         dist.barrier()
+    # Fused shared expert together with expert parallelism: every rank applies the
+    # (replicated) shared expert to its own tokens while its routes go to their owners.
+    if not failures:
+        sbuf = G.get_symm_buffer_for_gc_moe(group, E, CAP, K, H, I, 1)
+        gs = torch.Generator().manual_seed(11)
+        sw1, sc1 = O.quantize_block_fp8(torch.randn((2 * I, H), generator=gs) * 0.02)
+        sw2, sc2 = O.quantize_block_fp8(torch.randn((H, I), generator=gs) * 0.02)
+        shared = {'w1': sw1, 'w1_codes': sc1, 'w2': sw2, 'w2_codes': sc2}
+        sl1, sl2 = G.transform_weights_for_gc_moe(
+            (sw1.to(dev), O.expand_block_sf_rows(sc1, 2 * I).to(dev)),
+            (sw2.to(dev), O.expand_block_sf_rows(sc2, H).to(dev)))
+        case = {'tokens': [(11 * (r + 2)) % 50 for r in range(world)], 'seed': 31}
+        all_inputs = [inputs_of(case, r) for r in range(world)]
+        bms = [G.get_block_m_for_gc_moe(world, E, CAP, case['tokens'][r], K) for r in range(world)]
+        ref = O.moe_layer([a[0] for a in all_inputs], [a[1] for a in all_inputs], [a[2] for a in all_inputs],
+                          [a[3] for a in all_inputs], *cpu_w, bms, clamp=10.0, shared=shared)
+        t = case['tokens'][rank]
+        xq, xsf, idx, w = all_inputs[rank]
+        sbuf.x[:t].copy_(xq.to(dev)); sbuf.x_sf[:t].copy_(xsf.to(dev))
+        sbuf.topk_idx[:t].copy_(idx.to(dev)); sbuf.topk_weights[:t].copy_(w.to(dev))
+        tt = torch.arange(t)
+        u = tt % bms[rank]
+        rows = (tt // bms[rank]) * ((bms[rank] + 127) // 128 * 128) + (u // 128) * 128 + (u % 32) * 4 + (u % 128) // 32
+        if t:
+            sbuf.shared_l1_acts_sf[rows.to(dev)] = xsf.to(dev)
+        y = torch.full((t, H), float('nan'), dtype=torch.bfloat16, device=dev)
+        torch.cuda.synchronize(); dist.barrier()
+        G.fp8_fp4_gc_moe(y, l1, l2, sbuf, sl1, sl2, activation_clamp=10.0, shared_recipe=(1, 128, 128))
+        torch.cuda.synchronize()
+        try:
+            sbuf.raise_on_device_error()
+            if t:
+                cos, err = O.cosine(y.cpu(), ref.y[rank]), O.max_rel_err(y.cpu(), ref.y[rank])
+                report['shared_expert'] = [round(cos, 9), err]
+                check('shared_expert:y', cos >= COSINE_MIN and err <= MAX_REL_ERR)
+        except RuntimeError as exc:
+            failures.append(f'shared_expert: {exc}')
+        dist.barrier()
+        sbuf.destroy()
     print(json.dumps({'rank': rank, 'world': world, 'failures': failures, 'y': report}), flush=True)
     buf.destroy()
     dist.destroy_process_group()
