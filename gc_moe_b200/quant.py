@@ -60,11 +60,21 @@ def quantize_weights_fp4(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return (nib[..., 0] | (nib[..., 1] << 4)).view(torch.int8), codes
 
 
+def _mn_major(words: torch.Tensor) -> torch.Tensor:
+    """Same values, memory MN-major: stride 1 along rows and `rows` along the
+    packed K axis (also when that axis has a single column)."""
+    *lead, rows, packs = words.shape
+    strides = [rows * packs * int(torch.tensor(lead[i + 1:]).prod()) if lead[i + 1:] else rows * packs
+               for i in range(len(lead))] + [1, rows]
+    out = torch.empty_strided(tuple(words.shape), tuple(strides), dtype=words.dtype, device=words.device)
+    out.copy_(words)
+    return out
+
+
 def weight_scales_mn_major(codes: torch.Tensor) -> torch.Tensor:
     """uint8 [E, rows, K/32] -> int32 [E, rows, K/128] stored MN-major, the
     form transform_weights_for_gc_moe expects."""
-    words = pack_scale_bytes(codes)
-    return words.transpose(-1, -2).contiguous().transpose(-1, -2)
+    return _mn_major(pack_scale_bytes(codes))
 
 
 def route(logits: torch.Tensor, topk: int) -> tuple[torch.Tensor, torch.Tensor]:
