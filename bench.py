@@ -108,6 +108,13 @@ class ClockSampler:
             if len(parts) == 6 and parts[0].isdigit():
                 self.samples.append(parts)
 
+    def wait_first(self, seconds: float) -> None:
+        """nvidia-smi needs a second or more to start on an 8-GPU box: do not begin
+        the timed region before it delivers samples."""
+        deadline = time.time() + seconds
+        while self.proc is not None and not self.samples and time.time() < deadline:
+            time.sleep(0.05)
+
     def __exit__(self, *exc):
         if self.proc is not None:
             time.sleep(0.1)
@@ -234,6 +241,7 @@ def run_ours(args):
 
     with torch.cuda.stream(stream):
         with ClockSampler(local_rank) as clocks:
+            clocks.wait_first(8.0)
             for s in range(args.warmup):
                 one_sweep(s, False)
             barrier()
