@@ -88,7 +88,7 @@ class ClockSampler:
               'clocks_event_reasons.sw_power_cap')
 
     def __init__(self, index: int):
-        self.index, self.samples, self.proc = index, [], None
+        self.index, self.samples, self.proc, self.first_timed = index, [], None, 0
 
     def __enter__(self):
         try:
@@ -115,6 +115,9 @@ class ClockSampler:
         while self.proc is not None and not self.samples and time.time() < deadline:
             time.sleep(0.05)
 
+    def mark_timed(self) -> None:
+        self.first_timed = len(self.samples)
+
     def __exit__(self, *exc):
         if self.proc is not None:
             time.sleep(0.1)
@@ -124,7 +127,8 @@ class ClockSampler:
     def summary(self) -> dict:
         if not self.samples:
             return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['unavailable']}
-        clocks = sorted(int(s[0]) for s in self.samples)
+        timed = self.samples[self.first_timed:] or self.samples     # samples during warm-up + timed region
+        clocks = sorted(int(s[0]) for s in timed)
         names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
         reasons = [n for i, n in enumerate(names) if any(s[2 + i] == 'Active' for s in self.samples)]
         return {'sm_mhz': clocks[len(clocks) // 2], 'sm_max_mhz': int(self.samples[0][1]),
@@ -242,6 +246,7 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         with ClockSampler(local_rank) as clocks:
             clocks.wait_first(8.0)
+            clocks.mark_timed()
             for s in range(args.warmup):
                 one_sweep(s, False)
             barrier()
