@@ -246,6 +246,7 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         with ClockSampler(local_rank) as clocks:
             clocks.wait_first(8.0)
+            barrier()                 # nvidia-smi starts at different speeds per rank: enter the loop together
             clocks.mark_timed()
             for s in range(args.warmup):
                 one_sweep(s, False)
