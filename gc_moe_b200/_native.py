@@ -57,6 +57,7 @@ _SIGNATURES = {
                                          ctypes.POINTER(ctypes.c_uint32)]),
     'gcmoe_launch_static_scratch': (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.POINTER(Buffers), ctypes.c_void_p]),
     'gcmoe_static_scratch_status': (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint32)]),
+    'gcmoe_debug_expire_wait': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p]),
     'gcmoe_debug_role_timing': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p]),
     'gcmoe_debug_gemm_l1_raw': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p]),
 }

@@ -26,6 +26,7 @@ struct CombineParams {
     // rows x tiles contributions have landed (null on a single rank)
     const uint32_t* call_info;     // [kCallInfoWords] written by the dispatch kernel
     const uint32_t* combine_arrived;   // this rank's exchange::kCombineArrived
+    uint32_t* failed;              // this rank's exchange::kFailed
     uint32_t* status;
     uint64_t timeout_ns;
     uint32_t tiles_per_row;        // H / 256: down-GEMM tiles that write one row
@@ -38,12 +39,14 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineP
     const uint64_t total = static_cast<uint64_t>(p.num_tokens) * vecs_per_token;
     ptx::launch_dependents();
     ptx::grid_dependency_wait();
+    if (*p.failed != 0u) return;     // an earlier wait on this workspace gave up: the host will raise
     if (p.num_ranks > 1) {
         __shared__ uint32_t abort_word;
         if (threadIdx.x == 0) {
             abort_word = 0;
             WaitCtl ctl;
             ctl.status = p.status;
+            ctl.failed = p.failed;
             ctl.abort = &abort_word;
             ctl.timeout_ns = p.timeout_ns;
             ctl.kernel = kKernelCombine;

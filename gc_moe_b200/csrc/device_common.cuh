@@ -33,6 +33,7 @@ enum KernelId : uint32_t { kKernelDispatch = 1, kKernelGemmL1 = 2, kKernelGemmL2
 
 struct WaitCtl {
     uint32_t* status;          // global status block
+    uint32_t* failed;          // workspace-wide sticky word: set once, every later kernel returns at once
     volatile uint32_t* abort;  // CTA-local abort word in shared memory
     uint64_t timeout_ns;
     uint32_t kernel;
@@ -48,6 +49,7 @@ __device__ __forceinline__ void report_failure(const WaitCtl& ctl, uint32_t code
         ctl.status[kStatusExpected] = expected;
         __threadfence();
     }
+    if (ctl.failed != nullptr) *ctl.failed = 1u;
     *ctl.abort = 1u;
 }
 
@@ -134,6 +136,7 @@ enum CallInfoWord : int {
 namespace exchange {
 constexpr uint32_t kCountsReady = 0;        // u32 [2][kMaxRanks]: epoch+1 once a source's counts landed
 constexpr uint32_t kSourceBlockM = 1024;    // u32 [2][kMaxRanks]: block-M each rank uses for its pool
+constexpr uint32_t kFailed = 1536;          // u32: a bounded wait of some call on this workspace ran out
 constexpr uint32_t kCombineArrived = 2048;  // u32 [2] (128 bytes apart): rows x tiles landed in combine_tokens
 constexpr uint32_t kRowsArrived = 4096;     // u32 [2][kMaxLocalExperts]: dispatched rows landed per local expert
 constexpr uint32_t kCounts = 8192;          // u32 [2][P][E]: routes of source s to global expert e

@@ -107,10 +107,14 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
 
     WaitCtl ctl;
     ctl.status = p.status;
+    ctl.failed = reinterpret_cast<uint32_t*>(my_arena + p.off_exchange + exchange::kFailed);
     ctl.abort = misc;
     ctl.timeout_ns = p.timeout_ns;
     ctl.kernel = kKernelDispatch;
 
+    // After a wait of an earlier call gave up the workspace's protocol state is void:
+    // do nothing (the host raises when it reads the status block) instead of waiting again.
+    if (*ctl.failed != 0u) return;
     for (uint32_t i = tid; i < 2 * E; i += kDispatchThreads) own[i] = 0;
     if (tid < 8) misc[tid] = 0;
     __syncthreads();

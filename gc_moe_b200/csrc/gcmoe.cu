@@ -167,15 +167,12 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
             b.sw2_sf_stride < uint64_t(q.hidden) || b.shared_sf_rows == 0)
             return fail(GCMOE_ERR_INVALID, "shared expert weights, scales or scale views missing or misaligned");
     }
-    if (q.num_ranks > 1) {
-        for (int r = 0; r < q.num_ranks; ++r)
-            if (b.arena_base[r] == 0 || b.arena_base[r] % 16)
-                return fail(GCMOE_ERR_INVALID, "arena of rank %d is not mapped", r);
-        if (b.off_exchange == 0 || b.off_exchange % 128 ||
-            exchange::bytes(q.num_ranks, q.num_experts) > (8u << 20))
-            return fail(GCMOE_ERR_INVALID, "exchange block missing or too small for %d ranks x %d experts",
-                        q.num_ranks, q.num_experts);
-    }
+    for (int r = 0; r < q.num_ranks; ++r)
+        if (b.arena_base[r] == 0 || b.arena_base[r] % 16)
+            return fail(GCMOE_ERR_INVALID, "arena of rank %d is not mapped", r);
+    if (b.off_exchange == 0 || b.off_exchange % 128 || exchange::bytes(q.num_ranks, q.num_experts) > (8u << 20))
+        return fail(GCMOE_ERR_INVALID, "exchange block missing or too small for %d ranks x %d experts",
+                    q.num_ranks, q.num_experts);
 
     GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
@@ -288,6 +285,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.num_ranks = P;
         g.call_info = call_info;
         g.rows_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kRowsArrived);
+        g.failed = reinterpret_cast<uint32_t*>(arena + b.off_exchange + exchange::kFailed);
         for (uint32_t r = 0; r < P; ++r) {
             g.combine_arrived[r] = b.arena_base[r] + b.off_exchange + exchange::kCombineArrived;
             g.combine_base[r] = b.arena_base[r] + b.off_combine_tokens;
@@ -445,6 +443,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     c.num_ranks = P;
     c.call_info = call_info;
     c.combine_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kCombineArrived);
+    c.failed = reinterpret_cast<uint32_t*>(arena + b.off_exchange + exchange::kFailed);
     c.status = plan->status;
     c.timeout_ns = timeout_ns;
     c.tiles_per_row = H / kTileRows;
@@ -534,6 +533,32 @@ extern "C" int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out
     grouped_gemm_kernel<false><<<grid, kGemmThreads, plan->gemm_smem, s>>>(g);
     GCMOE_CUDA(cudaGetLastError());
     return int(grid);
+}
+
+// A wait on a word nothing ever sets, with a short limit: exercises the timeout
+// path (status block, sticky word, clean return) without any real failure.
+__global__ void expire_wait_kernel(const uint32_t* never_set, uint32_t* status, uint32_t* failed,
+                                   uint64_t timeout_ns) {
+    __shared__ uint32_t abort_word;
+    abort_word = 0;
+    WaitCtl ctl;
+    ctl.status = status;
+    ctl.failed = failed;
+    ctl.abort = &abort_word;
+    ctl.timeout_ns = timeout_ns;
+    ctl.kernel = kKernelDispatch;
+    flag_wait_eq(never_set, 0xFFFFFFFFu, ctl, 99);
+}
+
+extern "C" int gcmoe_debug_expire_wait(gcmoe_plan* plan, unsigned timeout_us, void* cuda_stream) {
+    if (plan == nullptr) return fail(GCMOE_ERR_INVALID, "null plan");
+    const uint64_t arena = plan->buf.arena_base[plan->prob.rank];
+    // word 7 of the status block is never written by any kernel and starts at zero
+    expire_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        plan->status + 7, plan->status,
+        reinterpret_cast<uint32_t*>(arena + plan->buf.off_exchange + exchange::kFailed), uint64_t(timeout_us) * 1000ull);
+    GCMOE_CUDA(cudaGetLastError());
+    return GCMOE_OK;
 }
 
 extern "C" int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream) {

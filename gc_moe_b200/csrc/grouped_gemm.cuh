@@ -136,6 +136,7 @@ struct GemmParams {
     // the combine contributions (down); unused on a single rank
     const uint32_t* call_info;        // [kCallInfoWords] written by the dispatch kernel
     const uint32_t* rows_arrived;     // this rank's exchange::kRowsArrived, [2][kMaxLocalExperts]
+    uint32_t* failed;                 // this rank's exchange::kFailed
     uint64_t combine_arrived[kMaxRanks];  // address of exchange::kCombineArrived on each rank
     uint32_t num_ranks;
     // ---- optional role timing: [grid][kTimingRoles][kTimingWords] clock64 totals, or null
@@ -288,6 +289,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
     WaitCtl ctl;
     ctl.status = p.status;
+    ctl.failed = p.failed;
     ctl.abort = abort_word;
     ctl.timeout_ns = p.timeout_ns;
     ctl.kernel = kKernelGemmL1;
@@ -353,7 +355,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const uint32_t tmem_base = *tmem_slot;
 
     const uint32_t bm = p.block_m;
-    const uint32_t total_tiles = seg_meta[4 + kMaxSegments];
+    // nothing to do once a wait of an earlier call on this workspace has given up
+    const uint32_t total_tiles = *p.failed != 0u ? 0u : seg_meta[4 + kMaxSegments];
 
     // Decode a tile index: segment, row block, 256-row weight slice, owning
     // expert (last e with start[e] <= block) and the block's valid rows.

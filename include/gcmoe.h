@@ -139,6 +139,13 @@ int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* words);
  * descriptor and scale plumbing. */
 int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream);
 
+/* Enqueue a one-thread kernel that waits, for at most `timeout_us`, on a word
+ * nothing sets: the wait runs out, the plan's status block and the workspace's
+ * sticky failure word are set, and the kernel returns.  Lets a test exercise
+ * failure detection on a healthy GPU; the reference's counterpart is the
+ * timeout path of comm/gc_barrier.py:44-80, which traps instead. */
+int gcmoe_debug_expire_wait(gcmoe_plan* plan, unsigned timeout_us, void* cuda_stream);
+
 /* Run the grouped GEMM launch (which = 0 gate/up tiles only, 1 down tiles only,
  * 2 both as in a layer call) with per-role
  * cycle counters written to `out`: uint64 [grid][5 roles][4] = {cycles in the

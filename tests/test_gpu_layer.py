@@ -298,3 +298,32 @@ def test_fused_shared_expert_k32(single_rank_group):
         assert_close(y.cpu(), ref.y[0])
     finally:
         case.close()
+
+
+def test_expired_wait_is_reported_and_later_calls_return_at_once(single_rank_group):
+    """Failure detection without a failure: a wait on a word nothing sets runs
+    out after 200 us, the status block says where, the host raises, and every
+    later kernel on the workspace returns immediately instead of waiting again."""
+    import ctypes
+    import gc_moe_b200 as G
+    from gc_moe_b200 import _native, operator
+    from gc_moe_b200.contract import validate_call
+    case = LayerCase(single_rank_group, num_experts=8, hidden=1024, inter=512, topk=2, seed=9)
+    try:
+        inputs = O.make_tokens(6, case.h, case.e, case.k, seed=70)
+        good = case.run(*inputs)
+        assert torch.isfinite(good.float()).all()
+        y = torch.full((6, case.h), float('nan'), dtype=torch.bfloat16, device='cuda')
+        cfg = validate_call(y, case.l1, case.l2, case.buf, None, None, None, (1, 1, 32), 'swiglu', 10.0, True,
+                            None, None)
+        plan = operator.get_plan(cfg, y, case.l1, case.l2, case.buf, None, None, None)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _native.raise_for(_native.library().gcmoe_debug_expire_wait(plan.handle, 200, stream))
+        torch.cuda.synchronize()
+        with pytest.raises(RuntimeError, match='device wait gave up'):
+            case.buf.raise_on_device_error()
+        G.fp8_fp4_gc_moe(y, case.l1, case.l2, case.buf, activation_clamp=10.0)   # returns at once, writes nothing
+        torch.cuda.synchronize()
+        assert torch.isnan(y.float()).all()
+    finally:
+        case.close()
