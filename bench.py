@@ -324,9 +324,9 @@ def run_ours(args):
                 'achieved': round(achieved, 1), 'peak': peak, 'peak_source': peak_src,
                 'unit': 'GB/s', 'frac': round(achieved / peak, 4),
                 'algorithmic_bytes': l1_bytes, 'launch_us': round(kernel_us['expert_gemms'], 2),
-                # ncu (profiles/): DRAM traffic is 1.016 x the algorithmic bytes at 32 tokens of
+                # ncu (profiles/): DRAM traffic is 1.014 x the algorithmic bytes at 32 tokens of
                 # the single-GPU config; traffic grows with the active experts
-                'traffic': round(l1_bytes * 1.016) if world == 1 else None,
+                'traffic': round(l1_bytes * 1.014) if world == 1 else None,
                 'layer_frac_by_tokens_rank0': {
                     str(tt): round(active[tt] * wl.expert_bytes() / (float(latency[str(tt)]) * 1e-6) / 1e9 / peak, 4)
                     for tt in sweep},
