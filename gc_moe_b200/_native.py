@@ -40,6 +40,13 @@ class Buffers(ctypes.Structure):
             'scratch', 'scratch_bytes', 'off_exchange')]
 
 
+class StageArgs(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_uint64) for name in (
+        'x', 'router_logits', 'topk_idx_in', 'topk_weights_in', 'x_q', 'x_sf', 'topk_idx',
+        'topk_weights', 'shared_sf')] + [(name, ctypes.c_uint32) for name in (
+            'shared_sf_rows', 'block_m', 'num_tokens', 'hidden', 'num_experts', 'topk')]
+
+
 LIBRARY_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'libgcmoe_sm100.so')
 
 # name -> (restype, argtypes); every symbol include/gcmoe.h declares.
@@ -55,6 +62,7 @@ _SIGNATURES = {
     'gcmoe_kernels_per_launch': (ctypes.c_int, [ctypes.c_void_p]),
     'gcmoe_status_read': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p,
                                          ctypes.POINTER(ctypes.c_uint32)]),
+    'gcmoe_stage_inputs': (ctypes.c_int, [ctypes.POINTER(StageArgs), ctypes.c_void_p]),
     'gcmoe_launch_static_scratch': (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.POINTER(Buffers), ctypes.c_void_p]),
     'gcmoe_static_scratch_status': (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint32)]),
     'gcmoe_debug_expire_wait': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p]),

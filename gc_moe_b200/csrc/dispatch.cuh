@@ -174,11 +174,11 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
 
     // Pool-block prefix and GEMM-tile prefix of every owner's local experts
     // (warp w: owners w, w+8, ...).  The GEMMs tile an expert's rows by
-    // gemm_tile_rows(BM) tokens, which is more than BM for small BM, so that an
-    // expert with many rows costs fewer passes over its weights.
+    // gemm_tile_rows(BM) tokens rather than by pool blocks, so that an expert with
+    // many rows costs fewer passes over its weights.
     for (uint32_t r = warp; r < P; r += kDispatchThreads / 32) {
         const uint32_t bm = bm_of[r], base = r * EL;
-        const uint32_t tn = p.private_sf_row ? gemm_tile_rows(bm) : bm;
+        const uint32_t tn = p.private_sf_row ? gemm_tile_rows(bm, p.shared_table != nullptr) : bm;
         const uint32_t per_lane = (EL + 31) / 32;
         uint32_t sum = 0, tsum = 0;
         for (uint32_t i = 0; i < per_lane; ++i) {
@@ -327,7 +327,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         const uint32_t sf_row = block * sf_block + sf_row_in_block(u);
         uint32_t* sf_dst = reinterpret_cast<uint32_t*>(dst_arena + p.off_l1_acts_sf);
         // second copy, ordered by GEMM tile, when the tiles are not the pool blocks
-        const uint32_t tn = p.private_sf_row ? gemm_tile_rows(bm) : bm;
+        const uint32_t tn = p.private_sf_row ? gemm_tile_rows(bm, p.shared_table != nullptr) : bm;
         const uint32_t pos = slice_pos[a - lo];
         const uint32_t tile_row = p.private_sf_row + (first_tile[e] + pos / tn) * round_up_u32(tn, 128) +
                                   sf_row_in_block(pos % tn);

@@ -8,6 +8,7 @@
 
 #include "../../include/gcmoe.h"
 #include "combine.cuh"
+#include "stage_inputs.cuh"
 #include "dispatch.cuh"
 #include "grouped_gemm.cuh"
 
@@ -206,13 +207,13 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     int* expert_row_start = expert_tile_start + EL + 1;
     uint32_t* call_info = reinterpret_cast<uint32_t*>(expert_row_start + EL);
 
-    // GEMM tiles of small block-M pools span several pool blocks (gemm_tile_rows); their
-    // scale words are then kept a second time, in tile order, in the upper half of every
+    // GEMM tiles need not be pool blocks (gemm_tile_rows); the
+    // scale words of such tiles are kept a second time, in tile order, in the upper half of every
     // plane of the scale rings, which the reference layout never touches for block-M >= 16.
     // Every rank must take the same decision: it depends on the buffer geometry only.
     const uint32_t private_sf_row =
         (uint64_t(q.ring_tokens) / 64 + EL + 1) * 128 <= uint64_t(q.sf_ring_tokens) / 2 ? uint32_t(q.sf_ring_tokens) / 2 : 0u;
-    const uint32_t tn = private_sf_row ? gemm_tile_rows(bm) : bm;     // rows per GEMM tile on this rank
+    const uint32_t tn = private_sf_row ? gemm_tile_rows(bm, q.num_shared_experts > 0) : bm;   // rows per GEMM tile on this rank
     const uint32_t sftn = round_up_u32(tn, 128);
 
     // ---- dispatch
@@ -299,7 +300,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         sg.row_start = expert_row_start;
         sg.experts = EL;
         sg.tile_rows = tn;
-        sg.narrow_rows = bm;          // tn == bm: both maps are the same box
+        sg.narrow_rows = bm < tn ? bm : tn;   // tiles with at most this many rows fetch the smaller box
         sg.sf_chunk_rows = sftn;
         sg.ref_block_m = bm;
         sg.out_sf_private = tn != bm ? private_sf_row : 0u;
@@ -316,7 +317,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         sg.w_sf_stride = uint32_t(w_sf_stride);
         const uint64_t adims[2] = {k, uint64_t(q.ring_tokens)};
         const uint64_t astr[1] = {k};
-        const uint32_t abox[2] = {128, tn}, nbox[2] = {128, bm};
+        const uint32_t abox[2] = {128, tn}, nbox[2] = {128, bm < tn ? bm : tn};
         if (int rc = encode_map(&sg.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
             return rc;
         if (int rc = encode_map(&sg.tm_act_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, nbox, what))
@@ -557,6 +558,45 @@ extern "C" int gcmoe_debug_expire_wait(gcmoe_plan* plan, unsigned timeout_us, vo
     expire_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
         plan->status + 7, plan->status,
         reinterpret_cast<uint32_t*>(arena + plan->buf.off_exchange + exchange::kFailed), uint64_t(timeout_us) * 1000ull);
+    GCMOE_CUDA(cudaGetLastError());
+    return GCMOE_OK;
+}
+
+extern "C" int gcmoe_stage_inputs(const gcmoe_stage_args* args, void* cuda_stream) {
+    if (args == nullptr) return fail(GCMOE_ERR_INVALID, "null argument");
+    const gcmoe_stage_args& a = *args;
+    if (a.num_tokens == 0) return GCMOE_OK;
+    if (a.hidden == 0 || a.hidden % 256) return fail(GCMOE_ERR_INVALID, "hidden must be a positive multiple of 256");
+    if (a.topk == 0 || a.topk > 32) return fail(GCMOE_ERR_INVALID, "topk must be in 1..32");
+    if (a.x == 0 || a.x % 16 || a.x_q == 0 || a.x_q % 8 || a.x_sf == 0 || a.x_sf % 4 || a.topk_idx == 0 ||
+        a.topk_idx % 8 || a.topk_weights == 0 || a.topk_weights % 4)
+        return fail(GCMOE_ERR_INVALID, "activation or output address missing or misaligned");
+    if (a.router_logits != 0) {
+        if (a.router_logits % 4 || a.num_experts < a.topk || a.num_experts > 2048)
+            return fail(GCMOE_ERR_INVALID, "router logits need topk <= num_experts <= 2048");
+    } else if (a.topk_idx_in == 0 || a.topk_idx_in % 8 || a.topk_weights_in == 0 || a.topk_weights_in % 4) {
+        return fail(GCMOE_ERR_INVALID, "neither router logits nor top-k arrays given");
+    }
+    if (a.shared_sf != 0 && (a.shared_sf % 4 || a.block_m == 0 || a.block_m % 16 ||
+                             uint64_t((a.num_tokens + a.block_m - 1) / a.block_m) * round_up_u32(a.block_m, 128) >
+                                 a.shared_sf_rows))
+        return fail(GCMOE_ERR_INVALID, "shared scale view too small for %u tokens in blocks of %u", a.num_tokens,
+                    a.block_m);
+    StageParams p;
+    p.x = reinterpret_cast<const uint4*>(a.x);
+    p.logits = reinterpret_cast<const float*>(a.router_logits);
+    p.idx_in = reinterpret_cast<const long long*>(a.topk_idx_in);
+    p.weights_in = reinterpret_cast<const float*>(a.topk_weights_in);
+    p.x_q = reinterpret_cast<uint2*>(a.x_q);
+    p.x_sf = reinterpret_cast<uint32_t*>(a.x_sf);
+    p.topk_idx = reinterpret_cast<long long*>(a.topk_idx);
+    p.topk_weights = reinterpret_cast<float*>(a.topk_weights);
+    p.shared_sf = reinterpret_cast<uint32_t*>(a.shared_sf);
+    p.shared_sf_rows = a.shared_sf_rows;
+    p.block_m = a.block_m;
+    p.hidden = a.hidden; p.num_experts = a.num_experts; p.topk = a.topk;
+    const size_t smem = a.router_logits != 0 ? size_t(a.num_experts) * 4 : 0;
+    stage_inputs_kernel<<<a.num_tokens, kStageThreads, smem, static_cast<cudaStream_t>(cuda_stream)>>>(p);
     GCMOE_CUDA(cudaGetLastError());
     return GCMOE_OK;
 }

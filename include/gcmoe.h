@@ -84,10 +84,10 @@ typedef struct gcmoe_buffers {
     uint64_t sw1_sf_stride, sw2_sf_stride;
     uint64_t scratch;             /* gcmoe_scratch_bytes() bytes, zero-filled    */
     uint64_t scratch_bytes;
-    uint64_t off_exchange;        /* multi-rank only: byte offset of 8 MiB of the
-                                   * arena for this library's own cross-rank
-                                   * counters; the reference layout's unused
-                                   * `l2_full_mask` signal region                */
+    uint64_t off_exchange;        /* required: byte offset of 8 MiB of the arena
+                                   * for this library's own cross-rank counters
+                                   * and its sticky failure word; the reference
+                                   * layout's unused `l2_full_mask` signal region */
 } gcmoe_buffers;
 
 typedef struct gcmoe_plan gcmoe_plan;
@@ -154,6 +154,35 @@ int gcmoe_debug_expire_wait(gcmoe_plan* plan, unsigned timeout_us, void* cuda_st
  * epilogue.  Returns the grid size.  Tuning aid; no counterpart in the
  * reference, which has no tracing (only printf on timeouts). */
 int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cuda_stream);
+
+/* Inputs of gcmoe_stage_inputs: device addresses and element counts. */
+typedef struct gcmoe_stage_args {
+    uint64_t x;               /* bf16 [T, H] activations, rows 16-byte aligned     */
+    uint64_t router_logits;   /* f32 [T, E], or 0 to copy the two arrays below     */
+    uint64_t topk_idx_in;     /* int64 [T, k]  (router_logits == 0)                */
+    uint64_t topk_weights_in; /* f32 [T, k]    (router_logits == 0)                */
+    uint64_t x_q;             /* out: e4m3 [cap, H]       = GCSymmBuffer.x          */
+    uint64_t x_sf;            /* out: int32 [cap, H/128]  = GCSymmBuffer.x_sf       */
+    uint64_t topk_idx;        /* out: int64 [cap, k]      = GCSymmBuffer.topk_idx   */
+    uint64_t topk_weights;    /* out: f32 [cap, k]        = GCSymmBuffer.topk_weights */
+    uint64_t shared_sf;       /* out: MN-major int32 [shared_sf_rows, H/128] =
+                               * GCSymmBuffer.shared_l1_acts_sf, or 0             */
+    uint32_t shared_sf_rows;
+    uint32_t block_m;         /* get_block_m_for_gc_moe(...) of the call (shared_sf) */
+    uint32_t num_tokens, hidden, num_experts, topk;
+} gcmoe_stage_args;
+
+/* Upstream producer of a layer call, one kernel on `cuda_stream`: picks the k
+ * largest router logits per token (descending, ties to the lower expert id)
+ * with softmax weights over those k, quantises the BF16 rows to e4m3 with one
+ * UE8M0 scale 2^ceil(log2(amax/448)) per 32 channels, and writes both straight
+ * into the workspace views, including the shared expert's scale rows at
+ * (t / BM) * align(BM,128) + (u & ~127) + (u & 31) * 4 + ((u >> 5) & 3),
+ * u = t % BM.  Replaces the four copy_ kernels, the quantise kernel and the
+ * index_put the reference leaves to the caller (README.md:234-252, 363-377;
+ * "the scale staging can be fused into an upstream producer", README.md:387).
+ * Allocates nothing; capturable. */
+int gcmoe_stage_inputs(const gcmoe_stage_args* args, void* cuda_stream);
 
 /* One layer call for callers that cannot allocate device memory (no
  * counterpart in the reference, whose launch path allocates through its JIT

@@ -162,3 +162,44 @@ def test_package_quantisers_equal_the_oracle_quantisers():
     assert torch.equal(a.view(torch.uint8), c.view(torch.uint8)) and torch.equal(b, d)
     assert torch.equal(O.pack_weight_sf_mn_major(d.view(torch.uint8).reshape(1, 5, -1)),
                        quant.weight_scales_mn_major(d.view(torch.uint8).reshape(1, 5, -1)))
+
+
+def test_route_topk_orders_by_value_then_expert_id():
+    logits = torch.tensor([[0.5, 2.0, 2.0, -1.0, 2.0, 0.5], [0.0] * 6])
+    idx, w = O.route_topk(logits, 4)
+    assert idx.tolist() == [[1, 2, 4, 0], [0, 1, 2, 3]]
+    assert torch.allclose(w.sum(-1), torch.ones(2))
+    assert torch.allclose(w[1], torch.full((4,), 0.25))
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn((50, 64), generator=g)
+    idx, w = O.route_topk(logits, 8)
+    top, ref_idx = torch.topk(logits, 8, dim=-1)          # distinct values: same selection
+    assert torch.equal(idx, ref_idx)
+    assert torch.allclose(w, torch.softmax(top, -1))
+
+
+def test_stage_shared_sf_rows_follow_the_block_order():
+    from gc_moe_b200.layout import sf_row_in_block
+    x_sf = torch.arange(300 * 8, dtype=torch.int32).reshape(300, 8)
+    for bm in (16, 96, 192):
+        rows_total = -(-300 // bm) * (-(-bm // 128) * 128)
+        staged, where = O.stage_shared_sf(x_sf, bm, rows_total)
+        assert len(set(where.tolist())) == 300
+        for t in (0, 1, 31, 32, 95, 96, 127, 128, 191, 192, 299):
+            row = (t // bm) * (-(-bm // 128) * 128) + sf_row_in_block(t % bm)
+            assert int(where[t]) == row
+            assert torch.equal(staged[row], x_sf[t])
+
+
+def test_integer_scale_rule_of_the_producer_kernel_equals_the_oracle_rule_for_every_bf16():
+    """The CUDA producer computes the UE8M0 code of amax/448 from the float's bits
+    (exponent, plus one when the mantissa exceeds 1.75, minus 8, floored at 0).
+    Exhaustive over all finite non-negative BF16 values."""
+    import numpy as np
+    hi = np.arange(0, 0x7F80, dtype=np.uint32)                 # all finite non-negative BF16 bit patterns
+    bits = hi << 16
+    amax = torch.from_numpy(bits.view(np.float32).copy())
+    up = (bits + 0x7FFFFF - 0x600000) >> 23
+    rule = np.maximum(up, 8) - 8
+    want = O.ue8m0_ceil_exponent(amax / O.E4M3_MAX).numpy()
+    assert np.array_equal(rule.astype(np.uint8), want)
