@@ -166,7 +166,7 @@ struct RoleTimer {
 };
 
 struct GemmSmemLayout {
-    uint32_t w, a, sfw, sfa, bars, tables, amax, rows, out, total;
+    uint32_t w, a, sfw, sfa, bars, tables, amax, arrive, rows, out, total;
 };
 
 __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint32_t block_m,
@@ -182,7 +182,8 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
     // TMEM base slot and the abort word
     l.tables = l.bars + (2 * stages + 6) * 8 + 16;
     l.amax = l.tables + round_up_u32((table_words + 16) * 4, 16);   // tables + per-segment offsets and tile prefix
-    l.rows = l.amax + 2 * 4 * 16 * 4;                 // amax exchange [2][4][16] floats
+    l.arrive = l.amax + 2 * 4 * 16 * 4;               // amax exchange [2][4][16] floats
+    l.rows = l.arrive + kMaxRanks * 4;                // rows x tiles written per source rank by this CTA
     l.out = round_up_u32(l.rows + 2 * block_m * 16, 16);   // per-block row info, double buffered
     l.total = l.out + 2 * 16 * kHalfRows * 2;          // output transpose: [2][16 tokens][128 channels] bf16
     return l;
@@ -281,6 +282,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     volatile uint32_t* const abort_word = tmem_slot + 1;
     int* const tables = reinterpret_cast<int*>(gbase + L.tables);
     float* const amax_x = reinterpret_cast<float*>(gbase + L.amax);       // [2][4][16]
+    uint32_t* const arrive = reinterpret_cast<uint32_t*>(gbase + L.arrive);  // [kMaxRanks]
     uint32_t* const row_info = reinterpret_cast<uint32_t*>(gbase + L.rows);  // [2][BM][4]
     __nv_bfloat16* const out_stage = reinterpret_cast<__nv_bfloat16*>(gbase + L.out);  // [2][16][128]
 
@@ -555,6 +557,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         bool ok = true;
         const float clamp_bf16 = __bfloat162float(__float2bfloat16_rn(p.clamp));
         RoleTimer timer(warp == 4 ? p.timing : nullptr, 4);
+        uint32_t weights_ready = 0xFFFFFFFFu;   // expert whose pushed route weights are known to have landed
+        for (uint32_t i = etid; i < kMaxRanks; i += 128) arrive[i] = 0;
+        epilogue_barrier();
         for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
             const TileCoord tc = locate(tile);
             const GemmSegment& sg = p.seg[tc.seg];
@@ -566,13 +571,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // Stage what the stores need to know about the block's rows while the
             // main loop is still running: route weight (gate/up) or destination.
             uint32_t* const info = row_info + (it & 1u) * bm * 4;
-            if (!kRaw && sg.kind == kSegUp && p.num_ranks > 1 && !sg.shared) {
+            if (!kRaw && sg.kind == kSegUp && p.num_ranks > 1 && !sg.shared && e != weights_ready) {
                 // Route weights are pushed by other GPUs together with the rows.
                 bool landed = true;
                 if (etid == 0)
                     landed = flag_wait_eq(p.rows_arrived + p.call_info[kCallGeneration] * kMaxLocalExperts + e,
                                           rows_of_expert(tc.seg, e), ctl, 6);
                 if (!all_epilogue_threads(landed)) { ok = false; break; }
+                weights_ready = e;
             }
             if (kRaw) {
             } else if (sg.kind == kSegUp) {
@@ -602,6 +608,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 break;
             }
             ptx::tc_fence_after();
+            if (!kRaw && sg.kind == kSegDown && p.num_ranks > 1 && !sg.shared) {
+                // Rows this tile writes to each source rank; reported once, after the
+                // CTA's last tile (the vote above made `info` visible to all threads).
+                for (uint32_t i = etid; i < valid; i += 128) atomicAdd(arrive + info[i * 3], 1u);
+            }
             for (uint32_t half = 0; half < 2; ++half)
             for (uint32_t c0 = 0; c0 < ncols; c0 += 16) {
                 const uint32_t nh = nt * 2 + half;      // index of the 128-row half among the expert's rows
@@ -726,24 +737,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     atomicAdd(sg.block_done + b, 1u);
                 }
             }
-            if (!kRaw && sg.kind == kSegDown && p.num_ranks > 1 && !sg.shared) {
-                // Tell each source rank how many of its rows this tile has written
-                // (rows of one source are contiguous in a block).  The barrier orders
-                // every epilogue thread's stores before the leader's release.
-                epilogue_barrier();
-                if (etid == 0) {
-                    const uint32_t gen = p.call_info[kCallGeneration];
-                    uint32_t run_rank = info[0], run = 0;
-                    for (uint32_t i = 0; i <= valid; ++i) {
-                        const uint32_t rk = i < valid ? info[i * 3] : 0xFFFFFFFFu;
-                        if (rk != run_rank) {
-                            ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(p.combine_arrived[run_rank] + gen * 128), run);
-                            run_rank = rk;
-                            run = 0;
-                        }
-                        ++run;
-                    }
-                }
+        }
+        if (!kRaw && ok && p.num_ranks > 1) {
+            // Tell each source rank how many rows x tiles this CTA has written into its
+            // combine slots: one release per rank and CTA, after the last tile.  A
+            // release per tile would make the epilogue wait for the NVLink round trip of
+            // its stores every time (measured: a third of the GEMM time on 4 GPUs).  The
+            // barrier orders every epilogue thread's stores before the releases.
+            epilogue_barrier();
+            if (etid < p.num_ranks) {
+                const uint32_t n = arrive[etid];
+                if (n != 0u)
+                    ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(p.combine_arrived[etid] +
+                                                                         p.call_info[kCallGeneration] * 128), n);
             }
         }
         timer.finish(it);
