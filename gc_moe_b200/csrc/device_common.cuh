@@ -125,7 +125,8 @@ enum CallInfoWord : int {
     kCallGeneration = 0,      // 0/1: which half of the double-buffered exchange this call uses
     kCallCombineRows = 1,     // valid routes of this rank = rows its combine waits for (per H/256 tile)
     kCallEpoch = 2,
-    kCallInfoWords = 4
+    kCallTileCursor = 4,      // tiles claimed by the running GEMM launch beyond one per CTA (back to 0 when it ends)
+    kCallInfoWords = 8
 };
 
 // Cross-rank exchange block: this library's own symmetric fields.  They live

@@ -138,9 +138,17 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             for (uint32_t e = tid; e < E; e += kDispatchThreads) counts[e] = own[e];
             if (tid == 0)
                 reinterpret_cast<uint32_t*>(ex + exchange::kSourceBlockM)[gen * kMaxRanks + p.rank] = p.block_m;
-            __syncthreads();
-            if (tid == 0) {
-                // the release is cumulative over the CTA's stores ordered before it by the barrier
+        }
+        __syncthreads();
+        // One thread per served peer raises that peer's flag, all at once: each release
+        // waits for the round trip of the stores above, so a loop over the peers would
+        // pay it once per peer (a CTA serves every peer when the call has few tokens).
+        // The releases are cumulative over the CTA's stores ordered before them by the
+        // barrier.
+        {
+            const uint32_t peer = blockIdx.x + tid * gridDim.x;
+            if (peer < P) {
+                uint8_t* const ex = reinterpret_cast<uint8_t*>(p.arena_base[peer]) + p.off_exchange;
                 ptx::st_release_sys(reinterpret_cast<uint32_t*>(ex + exchange::kCountsReady) + gen * kMaxRanks + p.rank,
                                     epoch + 1u);
             }

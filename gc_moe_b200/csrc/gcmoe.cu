@@ -285,6 +285,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.rank = q.rank;
         g.num_ranks = P;
         g.call_info = call_info;
+        g.tile_cursor = call_info + kCallTileCursor;
         g.rows_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kRowsArrived);
         g.failed = reinterpret_cast<uint32_t*>(arena + b.off_exchange + exchange::kFailed);
         for (uint32_t r = 0; r < P; ++r) {
@@ -674,8 +675,10 @@ extern "C" int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const g
     gcmoe_plan* plan = nullptr;
     if (int rc = gcmoe_plan_create(problem, &with_scratch, &plan)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-    // The array keeps what the previous call left: the status words must start at zero.
+    // The array keeps what the previous call left: the status words must start at zero,
+    // and so must the GEMM launch's tile cursor, whose place depends on the geometry.
     cudaError_t err = cudaMemsetAsync(scratch, 0, kStatusWords * 4, s);
+    if (err == cudaSuccess) err = cudaMemsetAsync(plan->fused.tile_cursor, 0, sizeof(uint32_t), s);
     int rc = err == cudaSuccess ? gcmoe_launch(plan, cuda_stream)
                                 : fail(GCMOE_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(err));
     gcmoe_plan_destroy(plan);   // host object only; the enqueued kernels carry their parameters by value

@@ -41,7 +41,7 @@
 
 namespace gcmoe {
 
-constexpr int kGemmThreads = 256;
+constexpr int kGemmThreads = 288;           // eight role warps and the tile scheduler warp
 constexpr int kHalfRows = 128;             // MMA M: rows of one accumulator
 constexpr int kTileRows = 256;             // weight rows per tile (two halves)
 constexpr int kTileK = 128;                // K per pipeline stage = 4 MMAs of K32
@@ -58,6 +58,7 @@ enum SegmentKind : uint32_t {
     kSegUp = 0,     // gate/up projection: SwiGLU, route weight, FP8 requantisation -> intermediate
     kSegDown = 1    // down projection: BF16 rows scattered to the source rank's combine slots
 };
+constexpr uint32_t kFeedSlots = 32;   // ring of claimed tiles per CTA; the roles are never more than ~8 tiles apart
 constexpr int kMaxSegments = 4;   // shared up, routed up, shared down, routed down
 
 // One grouped problem of a launch: the up or the down projection of the routed
@@ -139,6 +140,7 @@ struct GemmParams {
     uint32_t* failed;                 // this rank's exchange::kFailed
     uint64_t combine_arrived[kMaxRanks];  // address of exchange::kCombineArrived on each rank
     uint32_t num_ranks;
+    uint32_t* tile_cursor;   // claims made so far by this launch's CTAs beyond their first tile (zero between launches)
     // ---- optional role timing: [grid][kTimingRoles][kTimingWords] clock64 totals, or null
     unsigned long long* timing;
 };
@@ -146,7 +148,7 @@ struct GemmParams {
 // Role timing slots (per CTA): cycles inside the role loop, cycles spent in
 // each of the role's waits.  Roles: 0 weight producer, 1 activation producer,
 // 2 MMA warp 0, 3 MMA warp 1, 4 epilogue (warp 4).
-constexpr int kTimingRoles = 5;
+constexpr int kTimingRoles = 6;    // five roles, then the CTA: globaltimer ns at entry, at the start of the roles, at exit
 constexpr int kTimingWords = 4;   // total, wait A, wait B, tiles
 
 struct RoleTimer {
@@ -166,7 +168,7 @@ struct RoleTimer {
 };
 
 struct GemmSmemLayout {
-    uint32_t w, a, sfw, sfa, bars, tables, amax, arrive, rows, out, total;
+    uint32_t w, a, sfw, sfa, bars, tables, amax, arrive, feed, rows, out, total;
 };
 
 __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint32_t block_m,
@@ -183,7 +185,8 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
     l.tables = l.bars + (2 * stages + 6) * 8 + 16;
     l.amax = l.tables + round_up_u32((table_words + 16) * 4, 16);   // tables + per-segment offsets and tile prefix
     l.arrive = l.amax + 2 * 4 * 16 * 4;               // amax exchange [2][4][16] floats
-    l.rows = l.arrive + kMaxRanks * 4;                // rows x tiles written per source rank by this CTA
+    l.feed = l.arrive + kMaxRanks * 4;                // rows x tiles written per source rank by this CTA
+    l.rows = l.feed + (kFeedSlots + 2) * 8;           // ring of claimed tiles {sequence number, tile}, producer position
     l.out = round_up_u32(l.rows + 2 * block_m * 16, 16);   // per-block row info, double buffered
     l.total = l.out + 2 * 16 * kHalfRows * 2;          // output transpose: [2][16 tokens][128 channels] bf16
     return l;
@@ -283,11 +286,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     int* const tables = reinterpret_cast<int*>(gbase + L.tables);
     float* const amax_x = reinterpret_cast<float*>(gbase + L.amax);       // [2][4][16]
     uint32_t* const arrive = reinterpret_cast<uint32_t*>(gbase + L.arrive);  // [kMaxRanks]
+    // Slot n % kFeedSlots holds {n + 1, n-th tile of this CTA}, written with one 8-byte store.
+    volatile uint2* const feed_ring = reinterpret_cast<volatile uint2*>(gbase + L.feed);   // [kFeedSlots]
+    volatile uint32_t* const feed_pos = reinterpret_cast<volatile uint32_t*>(gbase + L.feed + kFeedSlots * 8);   // tiles the weight producer has started
     uint32_t* const row_info = reinterpret_cast<uint32_t*>(gbase + L.rows);  // [2][BM][4]
     __nv_bfloat16* const out_stage = reinterpret_cast<__nv_bfloat16*>(gbase + L.out);  // [2][16][128]
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
+    unsigned long long* const cta_times =
+        p.timing != nullptr && threadIdx.x == 0 ? p.timing + (static_cast<size_t>(blockIdx.x) * kTimingRoles + 5) * kTimingWords : nullptr;
+    if (cta_times) cta_times[0] = ptx::globaltimer_ns();
 
     WaitCtl ctl;
     ctl.status = p.status;
@@ -307,6 +316,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             ptx::mbar_init(bar_drain + 8 * i, 1);
         }
         *abort_word = 0;
+        for (uint32_t i = 0; i < kFeedSlots; ++i) { feed_ring[i].x = 0; feed_ring[i].y = 0; }
+        *feed_pos = 0;
         ptx::fence_mbar_init();
         for (uint32_t g = 0; g < p.num_segments; ++g) {
             ptx::prefetch_tensormap(&p.seg[g].tm_act);
@@ -355,6 +366,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     __syncthreads();
     const uint32_t tmem_base = *tmem_slot;
+    if (cta_times) cta_times[1] = ptx::globaltimer_ns();
 
     const uint32_t bm = p.block_m;
     // nothing to do once a wait of an earlier call on this workspace has given up
@@ -388,6 +400,48 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         return static_cast<uint32_t>(tables[seg_meta[seg] + p.seg[seg].experts + 1 + e]);
     };
 
+    // ---- tile feed.  The first tile of CTA c is tile c; the rest of the work list
+    // is claimed tile by tile from a counter all CTAs of the launch share (tiles cost
+    // different times: gate/up tiles have 2-3.5x the K of down tiles, and row counts
+    // differ).  The scheduler warp claims one tile ahead of the weight producer --
+    // so that the counter's round trip is on nobody's critical path, and no CTA
+    // hoards tiles -- and publishes the claims in a small ring in shared memory
+    // that the roles follow.  A CTA's claims ascend, and every gate/up tile comes
+    // before every down tile in the list, so when a down tile is claimed all the
+    // gate/up tiles it waits for are already claimed by running CTAs.
+    // The n-th tile of this CTA, for a whole warp (lane 0 polls): the tile index,
+    // total_tiles after the last one, 0xFFFFFFFF if the CTA is aborting.  Sequence
+    // number and tile travel in one 8-byte shared-memory word, so no fence is needed.
+    auto feed_take = [&](uint32_t n) -> uint32_t {
+        uint32_t t = 0xFFFFFFFFu;
+        if (lane == 0) {
+            volatile uint2* const slot = feed_ring + n % kFeedSlots;
+            uint32_t seq, tile;
+            auto read = [&]() {
+                asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];"
+                             : "=r"(seq), "=r"(tile) : "r"(ptx::smem_u32(const_cast<uint2*>(slot))) : "memory");
+            };
+            read();
+            if (seq != n + 1) {
+                const uint64_t t0 = ptx::globaltimer_ns();
+                uint32_t spins = 0;
+                for (;;) {
+                    read();
+                    if (seq == n + 1) break;
+                    if ((++spins & 63u) == 0u) {
+                        if (*ctl.abort) break;
+                        if (ptx::globaltimer_ns() - t0 > ctl.timeout_ns) {
+                            report_failure(ctl, kWaitTimeout, 7, seq, n + 1);
+                            break;
+                        }
+                    }
+                }
+            }
+            if (seq == n + 1) t = tile;
+        }
+        return __shfl_sync(0xffffffffu, t, 0);
+    };
+
     if (warp == 0 || warp == 2) {
         // ------------------------------------------------------------ producers
         const bool weights = warp == 0;
@@ -395,7 +449,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         uint32_t armed = 0, armed_parity = 0, ntiles = 0, ready_expert = 0xFFFFFFFFu;
         bool ok = true;
         RoleTimer timer(p.timing, weights ? 0 : 1);
-        for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++ntiles) {
+        for (; ok; ++ntiles) {
+            if (weights && lane == 0) *feed_pos = ntiles + 1;     // lets the scheduler claim the tile after this one
+            const uint32_t tile = feed_take(ntiles);
+            if (tile == 0xFFFFFFFFu) ok = false;
+            if (tile >= total_tiles) break;
             const TileCoord tc = locate(tile);
             const GemmSegment& sg = p.seg[tc.seg];
             const uint32_t b = tc.block, nt = tc.n_tile, e = tc.expert;
@@ -493,7 +551,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             uint32_t it = 0;
             bool ok = true;
             RoleTimer timer(p.timing, 2 + m);
-            for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+            for (; ok; ++it) {
+                const uint32_t tile = feed_take(it);
+                if (tile == 0xFFFFFFFFu) ok = false;
+                if (tile >= total_tiles) break;
                 const TileCoord tc = locate(tile);
                 const GemmSegment& sg = p.seg[tc.seg];
                 const uint32_t n = round_up_u32(tc.valid, 16);
@@ -546,6 +607,44 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 while (!ptx::mbar_try_wait(bar_drain + 8 * m, 0) && ptx::globaltimer_ns() - t0 < 2000000ull) {}
             }
         }
+    } else if (warp == 8) {
+        // ------------------------------------------------------------ tile scheduler
+        if (lane == 0) {
+            for (uint32_t n = 0;; ++n) {
+                // stay one tile ahead of the weight producer, not more
+                bool go = true;
+                if (n > *feed_pos) {
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while (n > *feed_pos) {
+                        __nanosleep(200);
+                        if (*ctl.abort) { go = false; break; }
+                        if (ptx::globaltimer_ns() - t0 > ctl.timeout_ns) {
+                            report_failure(ctl, kWaitTimeout, 8, *feed_pos, n);
+                            go = false;
+                            break;
+                        }
+                    }
+                }
+                if (!go) break;
+                uint32_t tile;
+                if (n == 0 && blockIdx.x < total_tiles) {
+                    tile = blockIdx.x;
+                } else {
+                    // Every CTA ends with exactly one claim beyond the list, so the launch
+                    // makes max(total - grid, 0) + grid claims; whoever draws the last one
+                    // knows all others are done claiming and puts the cursor back to zero
+                    // for the next launch.
+                    const uint32_t v = atomicAdd(p.tile_cursor, 1u);
+                    tile = min(gridDim.x + v, total_tiles);
+                    const uint32_t inside = total_tiles > gridDim.x ? total_tiles - gridDim.x : 0u;
+                    if (v == inside + gridDim.x - 1u) *p.tile_cursor = 0;
+                }
+                asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};"
+                             :: "r"(ptx::smem_u32(const_cast<uint2*>(feed_ring + n % kFeedSlots))), "r"(n + 1), "r"(tile)
+                             : "memory");
+                if (tile >= total_tiles) break;
+            }
+        }
     } else {
         // ------------------------------------------------------------ epilogue
         const uint32_t q = warp & 3u;           // the TMEM lane quarter this warp can read
@@ -560,7 +659,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         uint32_t weights_ready = 0xFFFFFFFFu;   // expert whose pushed route weights are known to have landed
         for (uint32_t i = etid; i < kMaxRanks; i += 128) arrive[i] = 0;
         epilogue_barrier();
-        for (uint32_t tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+        for (; ok; ++it) {
+            // The four warps read the same ring entry; they vote so that all of them
+            // leave together if one saw the CTA aborting (the named barriers below
+            // count 128 threads).
+            const uint32_t tile = feed_take(it);
+            if (!all_epilogue_threads(tile != 0xFFFFFFFFu)) { ok = false; break; }
+            if (tile >= total_tiles) break;
             const TileCoord tc = locate(tile);
             const GemmSegment& sg = p.seg[tc.seg];
             const uint32_t b = tc.block, nt = tc.n_tile, e = tc.expert, valid = tc.valid;
@@ -762,6 +867,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, p.tmem_cols);
     }
+    if (cta_times) cta_times[2] = ptx::globaltimer_ns();
 }
 
 }  // namespace gcmoe

@@ -148,10 +148,11 @@ int gcmoe_debug_expire_wait(gcmoe_plan* plan, unsigned timeout_us, void* cuda_st
 
 /* Run the grouped GEMM launch (which = 0 gate/up tiles only, 1 down tiles only,
  * 2 both as in a layer call) with per-role
- * cycle counters written to `out`: uint64 [grid][5 roles][4] = {cycles in the
- * role loop, cycles in its first wait, cycles in its second wait, tiles};
- * roles: weight producer, activation producer, MMA warp 0, MMA warp 1,
- * epilogue.  Returns the grid size.  Tuning aid; no counterpart in the
+ * cycle counters written to `out`: uint64 [grid][6][4]; entries 0-4 = {cycles
+ * in the role loop, cycles in its first wait, cycles in its second wait, tiles}
+ * of the weight producer, activation producer, MMA warp 0, MMA warp 1 and
+ * epilogue; entry 5 = the CTA's global-timer nanoseconds at kernel entry, at
+ * the start of the roles and at exit.  Returns the grid size.  Tuning aid; no counterpart in the
  * reference, which has no tracing (only printf on timeouts). */
 int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cuda_stream);
 
@@ -200,8 +201,9 @@ int gcmoe_stage_inputs(const gcmoe_stage_args* args, void* cuda_stream);
  *
  * The first call on a device looks up the array's device address; make that
  * first call before starting any stream capture on that device.  All calls on
- * a device share the one array: its status words are cleared on the stream
- * before the kernels, the rest is rewritten by the dispatch kernel, and two
+ * a device share the one array: its status words and the GEMM launch's tile
+ * cursor are cleared on the stream before the kernels, the rest is rewritten
+ * by the dispatch kernel, and two
  * calls whose kernels overlap on the GPU (different streams) race on it. */
 int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
                                 void* cuda_stream);
