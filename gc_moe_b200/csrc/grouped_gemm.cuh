@@ -2,10 +2,11 @@
 //
 //   out[weight_row, token] = sum_k W[e][weight_row, k] * X[token, k]
 //
-// per pool block (BM tokens of one local expert) and 256-row weight tile.
-// Weights are the MMA's A operand (two M = 128 halves per tile), tokens its B
-// operand (N = BM, a multiple of 16), so decode-sized token counts waste no
-// tensor rows and the HBM stream is the weight stream.  Roles (256 threads):
+// per row tile (up to gemm_tile_rows(BM) consecutive tokens of one local expert)
+// and 256-row weight tile.  Weights are the MMA's A operand (two M = 128
+// halves per tile), tokens its B operand (N = the tile's rows rounded up to
+// 16), so decode-sized token counts waste no tensor rows and the HBM stream is
+// the weight stream.  Roles (288 threads):
 //   warp 0    weight producer: per K128 stage one TMA tile of 256 rows (16 KiB
 //             of packed FP4, unpacked to 8-bit containers on the fly) + one
 //             bulk copy of its scale words
@@ -20,19 +21,23 @@
 //             allocation.
 //   warp 4-7  epilogue: read the FP32 accumulators from TMEM (each warp its own
 //             32-lane quarter), fuse the layer's element-wise tail, store
+//   warp 8    tile scheduler: claims this CTA's next tile from a cursor all
+//             CTAs share, one tile ahead of the weight producer
 // Every async instruction is issued under elect.sync by a converged warp: the
 // compiler then feeds TMA / tcgen05 operands from uniform registers, which
 // measured 1.5x faster than the same code under `lane == 0`.
 // Two accumulator stages let the epilogue of tile i overlap the main loop of
-// tile i+1.  The work list is static: tile t = pool_block * n_tiles + n_tile,
-// CTA c takes t = c, c + grid, ... so the CTAs that share a pool block run at
-// the same time and its activation tile is served from L2.
+// tile i+1.  The work list is tile t = row_tile * n_tiles + n_tile over the
+// segments [shared up | routed up | shared down | routed down]; CTA c starts on
+// tile c and then takes whatever tile is next, so the CTAs that share a row
+// tile run at about the same time and its activation tile is served from L2.
 //
 // Replaces the reference's role-2 compute kernel
 // (gc_moe/impls/sm100_fp8_fp4_gc_moe.py:1108-1905) and its device scheduler
-// (gc_moe/scheduler/gc_moe.py:284-328) for a design whose producers have
-// finished before this kernel starts (stream order), so it needs no task
-// hand-off and no ring flow control.
+// (gc_moe/scheduler/gc_moe.py:284-328) for a design whose local dispatch has
+// finished before this kernel starts (stream order), so it needs no ring flow
+// control; what it waits for are rows pushed by other GPUs (per-expert arrival
+// counters) and, for down tiles, the up tiles of the same rows.
 #pragma once
 
 #include <cuda_bf16.h>
