@@ -81,3 +81,24 @@ def route(logits: torch.Tensor, topk: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Top-k expert ids (int64) and softmax-over-the-selected-k weights (f32)."""
     top, idx = torch.topk(logits.float(), topk, dim=-1, sorted=False)
     return idx.to(torch.int64), torch.softmax(top, dim=-1)
+
+
+def quantize_weights_fp8_blocks(w: torch.Tensor, block: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
+    """[rows, K] -> (e4m3 [rows, K], uint8 scale bytes [rows/block, K/block]):
+    one UE8M0 scale per block x block tile, the shared expert's K128 recipe
+    (tests/test_gc_moe_se.py:69-71)."""
+    rows, k = w.shape
+    tiles = w.float().reshape(rows // block, block, k // block, block)
+    codes = _scale_exponent_byte(tiles.abs().amax(dim=(1, 3)) / E4M3_MAX)
+    scale = torch.exp2(codes.float() - 127.0)[:, None, :, None]
+    q = (tiles / scale).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return q.reshape(rows, k), codes
+
+
+def expand_block_scales(codes: torch.Tensor, rows: int, block: int = 128) -> torch.Tensor:
+    """Block-row scale bytes [rows/block, K/block] -> one packed int32 scale row
+    per output row, MN-major [rows, ceil(K/block/4)]: the form
+    transform_weights_for_gc_moe expects for K128 shared weights
+    (README.md:347-351)."""
+    per_row = codes.repeat_interleave(block, 0)[:rows]
+    return _mn_major(pack_scale_bytes(per_row))

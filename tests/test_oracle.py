@@ -203,3 +203,26 @@ def test_integer_scale_rule_of_the_producer_kernel_equals_the_oracle_rule_for_ev
     rule = np.maximum(up, 8) - 8
     want = O.ue8m0_ceil_exponent(amax / O.E4M3_MAX).numpy()
     assert np.array_equal(rule.astype(np.uint8), want)
+
+
+def test_package_weight_front_end_matches_the_oracle():
+    """The product-side helpers that bring checkpoint-style tensors into the
+    operator's input form produce the oracle's bytes."""
+    from gc_moe_b200 import quant
+    g = torch.Generator().manual_seed(21)
+    w = torch.randn((256, 512), generator=g) * 0.02
+    q, codes = quant.quantize_weights_fp8_blocks(w)
+    oq, ocodes = O.quantize_block_fp8(w)
+    assert torch.equal(q.view(torch.uint8), oq.view(torch.uint8)) and torch.equal(codes, ocodes)
+    a, b = quant.expand_block_scales(codes, 256), O.expand_block_sf_rows(ocodes, 256)
+    assert torch.equal(a, b) and a.stride() == b.stride() and a.stride(0) == 1
+    w4 = torch.randn((3, 64, 256), generator=g) * 0.02
+    p, c = quant.quantize_weights_fp4(w4)
+    op, oc = O.quantize_weight_fp4(w4)
+    assert torch.equal(p, op) and torch.equal(c, oc)
+    s, os_ = quant.weight_scales_mn_major(c), O.pack_weight_sf_mn_major(oc)
+    assert torch.equal(s, os_) and s.stride() == os_.stride()
+    x = (torch.randn((9, 512), generator=g)).to(torch.bfloat16)
+    xq, xsf = quant.quantize_activations(x)
+    oxq, oxsf = O.quantize_act_fp8(x)
+    assert torch.equal(xq.view(torch.uint8), oxq.view(torch.uint8)) and torch.equal(xsf, oxsf)
