@@ -233,11 +233,13 @@ def _stage_shared_sf(case, xsf, tokens, bm):
     view[rows.to('cuda')] = xsf.to('cuda')
 
 
-@pytest.mark.parametrize('tokens', [1, 16, 64, 200])
+@pytest.mark.parametrize('tokens', [1, 16, 64, 200, 1500])
 def test_fused_shared_expert_k128(single_rank_group, tokens):
     """Routed experts plus one fused shared expert (two experts' worth of
     intermediate) whose FP8 weights carry one UE8M0 scale per 128 x 128 block,
-    expanded to one packed row per output row before the transform."""
+    expanded to one packed row per output row before the transform.  1500
+    tokens give block-M 240: with a shared expert such blocks stay whole GEMM
+    tiles (one accumulator stage), a path no other case reaches."""
     import gc_moe_b200 as G
     e, h, i, k, s = 8, 1024, 512, 2, 2
     case = LayerCase(single_rank_group, e, h, i, k, seed=6, num_shared_experts=s)
