@@ -67,3 +67,24 @@ def test_version_and_argument_errors_need_no_gpu(lib):
     rc = lib.gcmoe_plan_create(ctypes.byref(prob), ctypes.byref(bufs), ctypes.byref(handle))
     assert rc == _native.ERR_INVALID and 'arena' in _native.last_error()
     assert lib.gcmoe_launch(None, None) == _native.ERR_INVALID
+
+
+def test_stage_inputs_struct_and_argument_errors_need_no_gpu(lib, tmp_path):
+    src = tmp_path / 'stage.c'
+    src.write_text('#include <stdio.h>\n#include "gcmoe.h"\nint main(void){printf("%zu %zu\\n",'
+                   'sizeof(gcmoe_stage_args),offsetof(gcmoe_stage_args,shared_sf_rows));return 0;}\n')
+    exe = tmp_path / 'stage'
+    subprocess.run(['gcc', '-I', os.path.join(ROOT, 'include'), str(src), '-o', str(exe)], check=True)
+    sizes = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    assert sizes == [ctypes.sizeof(_native.StageArgs), _native.StageArgs.shared_sf_rows.offset]
+
+    assert lib.gcmoe_stage_inputs(None, None) == _native.ERR_INVALID
+    good = dict(x=0x1000, router_logits=0x2000, x_q=0x3000, x_sf=0x4000, topk_idx=0x5000, topk_weights=0x6000,
+                num_tokens=4, hidden=1024, num_experts=8, topk=2, block_m=16)
+    for bad in (dict(hidden=1000), dict(topk=0), dict(topk=33), dict(x=0x1004), dict(x_q=0), dict(num_experts=1),
+                dict(num_experts=4096), dict(router_logits=0), dict(shared_sf=0x7000, shared_sf_rows=64, num_tokens=200),
+                dict(shared_sf=0x7000, shared_sf_rows=128, block_m=24)):
+        args = _native.StageArgs(**{**good, **bad})
+        assert lib.gcmoe_stage_inputs(ctypes.byref(args), None) == _native.ERR_INVALID, bad
+    # no tokens: nothing to do, nothing launched
+    assert lib.gcmoe_stage_inputs(ctypes.byref(_native.StageArgs(**{**good, 'num_tokens': 0})), None) == 0
