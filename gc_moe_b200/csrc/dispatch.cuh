@@ -290,7 +290,21 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             for (uint32_t j = 0; j < a - lo; ++j) i += (slice_expert[j] == e);
             const uint32_t owner = static_cast<uint32_t>(e) / EL;
             const uint32_t l = static_cast<uint32_t>(e) - owner * EL;
-            row = first_block[e] * bm_of[owner] + lower[e] + i;
+            // Position inside the expert's rows: sources one after the other up to
+            // 8 ranks; above that the sources are interleaved (round j takes the j-th
+            // route of every source that has more than j, sources ascending), the
+            // reference's order for large groups (impls/sm100_fp8_fp4_gc_moe.py:954-986).
+            uint32_t pos = lower[e] + i;
+            if (P > 8) {
+                const uint32_t* const counts = reinterpret_cast<const uint32_t*>(my_arena + p.off_exchange + exchange::kCounts) +
+                                               static_cast<size_t>(gen) * P * E + e;
+                pos = 0;
+                for (uint32_t s = 0; s < P; ++s) {
+                    const uint32_t c = counts[static_cast<size_t>(s) * E];
+                    pos += min(c, i) + ((s < p.rank && c > i) ? 1u : 0u);
+                }
+            }
+            row = first_block[e] * bm_of[owner] + pos;
             uint8_t* const dst_arena = reinterpret_cast<uint8_t*>(p.arena_base[owner]);
             if (i < p.capacity)
                 reinterpret_cast<uint32_t*>(dst_arena + p.off_index_table)[

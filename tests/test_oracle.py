@@ -226,3 +226,42 @@ def test_package_weight_front_end_matches_the_oracle():
     xq, xsf = quant.quantize_activations(x)
     oxq, oxsf = O.quantize_act_fp8(x)
     assert torch.equal(xq.view(torch.uint8), oxq.view(torch.uint8)) and torch.equal(xsf, oxsf)
+
+
+@pytest.mark.parametrize('ranks', [4, 12])
+def test_push_plan_agrees_with_the_pool_order_also_above_eight_ranks(ranks):
+    """Every source's own computation of its routes' pool rows lands exactly on the
+    rows the world-level dispatch assigns: concatenated sources up to 8 ranks,
+    interleaved sources (round j = j-th route of every source that has one) above."""
+    import numpy as np
+    experts, k, h = 2 * ranks, 3, 256
+    g = torch.Generator().manual_seed(ranks)
+    tokens = [int(torch.randint(0, 40, (1,), generator=g)) for _ in range(ranks)]
+    tokens[1] = 0                                              # an idle rank
+    idx = [torch.stack([torch.randperm(experts, generator=g)[:k] for _ in range(t)]) if t else
+           torch.zeros((0, k), dtype=torch.int64) for t in tokens]
+    idx[0][0, 0] = -1                                          # an invalid route
+    xb = [torch.randint(0, 255, (t, h), generator=g, dtype=torch.uint8).numpy() for t in tokens]
+    xsf = [torch.randint(0, 1 << 20, (t, h // 128), generator=g, dtype=torch.int32).numpy() for t in tokens]
+    w = [torch.rand((t, k), generator=g).numpy() for t in tokens]
+    bms = [16 if r % 2 else 32 for r in range(ranks)]
+    world = O.dispatch([i.numpy() for i in idx], w, xb, xsf, experts, bms)
+    counts = np.zeros((ranks, experts), np.int64)
+    for s in range(ranks):
+        flat = idx[s].reshape(-1)
+        for e in flat[(flat >= 0) & (flat < experts)].tolist():
+            counts[s, e] += 1
+    covered = [set() for _ in range(ranks)]
+    for s in range(ranks):
+        for owner, l, row, i, t, slot in O.push_plan(s, idx[s].numpy(), counts, bms, experts):
+            assert tuple(world[owner].metadata[row]) == (s, t, slot)
+            assert world[owner].index_lists[(l, s)][i] == t * k + slot
+            assert row not in covered[owner]
+            covered[owner].add(row)
+    for r in range(ranks):
+        assert covered[r] == set(np.nonzero(world[r].metadata[:, 0] >= 0)[0].tolist())
+    if ranks > 8:
+        # interleaving: inside an expert with several sources the first rows alternate sources
+        d = world[0]
+        srcs = d.metadata[:, 0]
+        assert any(srcs[i] >= 0 and srcs[i + 1] >= 0 and srcs[i + 1] < srcs[i] for i in range(len(srcs) - 1))
