@@ -287,32 +287,28 @@ def run_ours(args):
             dist.all_reduce(loc, op=dist.ReduceOp.MAX)
         b2b = {str(t): round(float(loc[j]), 2) for j, t in enumerate(sweep)}
 
-    # ---- per-kernel timing of the dominant kernel (gate/up GEMM) for the roofline.
-    # After a complete call the cross-rank counters of that call stay satisfied, so a
-    # single kernel of the layer can be launched again on its own.
+    # ---- per-kernel timing for the roofline: one complete layer call enqueued as three
+    # separate launches (dispatch | expert GEMMs | combine), which therefore run one after
+    # the other instead of overlapping as they do inside a layer call.
     t = ROOFLINE_TOKENS if ROOFLINE_TOKENS in sweep else sweep[-1]
     cstream = ctypes.c_void_p(stream.cuda_stream)
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    kernel_us = {}
+    kev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    parts = {'dispatch': [], 'expert_gemms': [], 'combine': []}
     with torch.cuda.stream(stream):
         stage(t, 0)
+        for _ in range(7):
+            barrier()
+            flush.zero_()
+            kev[0].record(stream)
+            for j, mask in enumerate((1, 6, 8)):
+                _native.raise_for(lib.gcmoe_launch_kernels(plans[t].handle, mask, cstream))
+                kev[j + 1].record(stream)
+            stream.synchronize()
+            for j, name in enumerate(parts):
+                parts[name].append(kev[j].elapsed_time(kev[j + 1]) * 1e3)
         barrier()
-        graphs[t].replay()
-        barrier()
-        kernels = (('expert_gemms', 6), ('gate_up_only', 2), ('down_only', 4))
-        if world == 1:
-            kernels += (('dispatch', 1), ('combine', 8))
-        for name, mask in kernels:
-            samples = []
-            for _ in range(5):
-                flush.zero_()
-                k0.record(stream)
-                lib.gcmoe_launch_kernels(plans[t].handle, mask, cstream)
-                k1.record(stream)
-                stream.synchronize()
-                samples.append(k0.elapsed_time(k1) * 1e3)
-            kernel_us[name] = sorted(samples)[len(samples) // 2]
-        barrier()
+    buf.raise_on_device_error()
+    kernel_us = {name: sorted(v[2:])[len(v[2:]) // 2] for name, v in parts.items()}
     peaks_path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
     if os.path.exists(peaks_path):
         peak, peak_src = float(json.load(open(peaks_path))['hbm_gbs']), 'measured'
@@ -324,9 +320,7 @@ def run_ours(args):
                 'achieved': round(achieved, 1), 'peak': peak, 'peak_source': peak_src,
                 'unit': 'GB/s', 'frac': round(achieved / peak, 4),
                 'algorithmic_bytes': l1_bytes, 'launch_us': round(kernel_us['expert_gemms'], 2),
-                # ncu (profiles/): DRAM traffic is 1.014 x the algorithmic bytes at 32 tokens of
-                # the single-GPU config; traffic grows with the active experts
-                'traffic': round(l1_bytes * 1.014) if world == 1 else None,
+                'traffic': None,
                 'layer_frac_by_tokens_rank0': {
                     str(tt): round(active[tt] * wl.expert_bytes() / (float(latency[str(tt)]) * 1e-6) / 1e9 / peak, 4)
                     for tt in sweep},

@@ -47,7 +47,9 @@ class StageArgs(ctypes.Structure):
             'shared_sf_rows', 'block_m', 'num_tokens', 'hidden', 'num_experts', 'topk')]
 
 
-LIBRARY_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'libgcmoe_sm100.so')
+# GC_MOE_B200_LIBRARY points at another build of the same library (a tuning variant).
+LIBRARY_PATH = os.environ.get('GC_MOE_B200_LIBRARY') or os.path.join(
+    os.path.dirname(os.path.abspath(__file__)), 'libgcmoe_sm100.so')
 
 # name -> (restype, argtypes); every symbol include/gcmoe.h declares.
 _SIGNATURES = {
@@ -66,7 +68,6 @@ _SIGNATURES = {
     'gcmoe_launch_static_scratch': (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.POINTER(Buffers), ctypes.c_void_p]),
     'gcmoe_static_scratch_status': (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint32)]),
     'gcmoe_debug_expire_wait': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p]),
-    'gcmoe_debug_role_timing': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_uint64, ctypes.c_void_p]),
     'gcmoe_debug_gemm_l1_raw': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p]),
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

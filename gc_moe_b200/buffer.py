@@ -88,6 +88,7 @@ class GCSymmBuffer:
             dist.barrier(group=group)
         _typed_views(self.buffer, self.layout, self)
         self._plans = {}          # launch plans cached per call signature
+        self._retired_scratch = []   # scratch blocks of evicted plans, until their status has been read
 
     def _for_call(self, num_shared_experts: int):
         """View of the same bytes laid out for the shared-expert count of one
@@ -128,12 +129,16 @@ class GCSymmBuffer:
         from . import operator
         for plan in list(self._plans.values()):
             operator.check_plan_status(plan)
+        retired, self._retired_scratch = self._retired_scratch, []
+        for scratch in retired:       # the status reads above have synchronised the stream
+            operator.check_retired_status(scratch)
 
     def destroy(self):
         from . import operator
         for plan in self._plans.values():
             operator.release_plan(plan)
         self._plans = {}
+        self._retired_scratch = []
         for name in self._views:
             setattr(self, name, None)
         self.peer_addresses = self.handle = self.buffer = self.group = None

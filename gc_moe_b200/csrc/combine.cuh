@@ -23,13 +23,13 @@ struct CombineParams {
     __nv_bfloat16* y;              // [T][H]
     uint32_t* epoch_word;          // per-call counter in the arena (recv_parity)
     // multi-rank: the partial rows are written by other GPUs; wait until
-    // rows x tiles contributions have landed (null on a single rank)
+    // rows x 128-channel pieces have landed (null on a single rank)
     const uint32_t* call_info;     // [kCallInfoWords] written by the dispatch kernel
     const uint32_t* combine_arrived;   // this rank's exchange::kCombineArrived
     uint32_t* failed;              // this rank's exchange::kFailed
     uint32_t* status;
     uint64_t timeout_ns;
-    uint32_t tiles_per_row;        // H / 256: down-GEMM tiles that write one row
+    uint32_t halves_per_row;       // H / 128: 128-channel pieces of a row, each counted once by its writer
     uint32_t num_ranks;
     uint32_t num_tokens, topk, hidden, capacity, num_experts, has_shared;
 };
@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineP
             ctl.timeout_ns = p.timeout_ns;
             ctl.kernel = kKernelCombine;
             flag_wait_eq(p.combine_arrived + p.call_info[kCallGeneration] * 32,
-                         p.call_info[kCallCombineRows] * p.tiles_per_row, ctl, 1);
+                         p.call_info[kCallCombineRows] * p.halves_per_row, ctl, 1);
         }
         __syncthreads();
     }

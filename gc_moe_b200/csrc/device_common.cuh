@@ -37,6 +37,7 @@ struct WaitCtl {
     volatile uint32_t* abort;  // CTA-local abort word in shared memory
     uint64_t timeout_ns;
     uint32_t kernel;
+    uint32_t peer_abort = 0;   // shared::cluster address of the other CTA's abort word (CTA pairs), or 0
 };
 
 __device__ __forceinline__ void report_failure(const WaitCtl& ctl, uint32_t code, uint32_t site,
@@ -51,6 +52,7 @@ __device__ __forceinline__ void report_failure(const WaitCtl& ctl, uint32_t code
     }
     if (ctl.failed != nullptr) *ctl.failed = 1u;
     *ctl.abort = 1u;
+    if (ctl.peer_abort != 0u) ptx::st_cluster_u32(ctl.peer_abort, 1u);   // the pair leaves together
 }
 
 // Wait for a phase of an mbarrier of this CTA.  Returns false when another
@@ -125,6 +127,8 @@ enum CallInfoWord : int {
     kCallGeneration = 0,      // 0/1: which half of the double-buffered exchange this call uses
     kCallCombineRows = 1,     // valid routes of this rank = rows its combine waits for (per H/256 tile)
     kCallEpoch = 2,
+    kCallTablesReady = 3,     // epoch + 1 once the tables of this call are in place (release by dispatch CTA 0):
+                              // the GEMM launch starts while the dispatch kernel is still pushing rows
     kCallTileCursor = 4,      // tiles claimed by the running GEMM launch beyond one per CTA (back to 0 when it ends)
     kCallInfoWords = 8
 };
@@ -137,38 +141,62 @@ enum CallInfoWord : int {
 namespace exchange {
 constexpr uint32_t kCountsReady = 0;        // u32 [2][kMaxRanks]: epoch+1 once a source's counts landed
 constexpr uint32_t kSourceBlockM = 1024;    // u32 [2][kMaxRanks]: block-M each rank uses for its pool
-constexpr uint32_t kFailed = 1536;          // u32: a bounded wait of some call on this workspace ran out
+constexpr uint32_t kFailed = 1920;          // u32: a bounded wait of some call on this workspace ran out
 constexpr uint32_t kCombineArrived = 2048;  // u32 [2] (128 bytes apart): rows x tiles landed in combine_tokens
 constexpr uint32_t kRowsArrived = 4096;     // u32 [2][kMaxLocalExperts]: dispatched rows landed per local expert
 constexpr uint32_t kCounts = 8192;          // u32 [2][P][E]: routes of source s to global expert e
+// every field ends before the next one begins, for the largest group the API admits
+static_assert(kCountsReady + 2u * kMaxRanks * 4u <= kSourceBlockM, "kCountsReady overlaps kSourceBlockM");
+static_assert(kSourceBlockM + 2u * kMaxRanks * 4u <= kFailed, "kSourceBlockM overlaps kFailed");
+static_assert(kFailed + 4u <= kCombineArrived, "kFailed overlaps kCombineArrived");
+static_assert(kCombineArrived + 128u + 4u <= kRowsArrived, "kCombineArrived overlaps kRowsArrived");
+static_assert(kRowsArrived + 2u * kMaxLocalExperts * 4u <= kCounts, "kRowsArrived overlaps kCounts");
 __host__ __device__ __forceinline__ uint32_t bytes(uint32_t ranks, uint32_t experts) {
     return kCounts + 2u * ranks * experts * 4u;
 }
 }  // namespace exchange
 
-// Rows (tokens) per GEMM tile for a pool laid out in blocks of `block_m`.  The
-// tiles are independent of the pool blocks (an expert's rows are contiguous):
-//  * small blocks are grouped up to 64 tokens, because a tcgen05.mma costs the
-//    same issue time for 16 columns as for 64;
-//  * blocks of 64 to 112 tokens are the tiles (measured: wider tiles for these
-//    cost a pipeline stage and gain nothing);
-//  * larger blocks (the large-token regime, block-M up to 240) are cut into
-//    tiles of 112 tokens, the largest count whose two accumulator stages and
-//    scale columns fit the 512 TMEM columns, so that the epilogue of one tile
-//    overlaps the MMAs of the next (measured at 4080 rows over 32 experts of
-//    H7168: 296 us instead of 472 us with whole 192-token blocks).
-// With a fused shared expert, whose scales the caller stages in block-M order,
-// the large blocks stay whole tiles.  Every rank evaluates this for every
-// owner, so it depends only on values all ranks share.
-constexpr uint32_t kWideTileRows = 112;
-__host__ __device__ __forceinline__ uint32_t gemm_tile_rows(uint32_t block_m, bool fused_shared) {
-    if (block_m < 64u) return 64u;
-    if (block_m <= kWideTileRows || fused_shared) return block_m;
-    return kWideTileRows;
-}
+// Two regimes of the expert GEMMs, chosen per rank from the block-M of its pool
+// (every sender knows every owner's block-M, so all ranks agree):
+//  * decode (block-M below 64): one CTA per tile, cta_group::1, tiles of up to 64
+//    tokens.  A tcgen05.mma costs the same issue time for 16 columns as for 64,
+//    and the kernel is bound by weight streaming and instruction issue.
+//  * large-token (block-M 64 and above): a CTA pair per tile, cta_group::2.  The
+//    pair's MMA covers 256 weight rows and up to 240 tokens with the token
+//    operand split over the two CTAs, so one fetch of a weight tile from shared
+//    memory serves twice the tokens a single CTA's 112-token tile could, and two
+//    accumulator stages of 240 columns fit each CTA's TMEM.
+// GEMM tiles are independent of the pool blocks: an expert's rows are contiguous
+// in the pool, and its tiles are sized from its own row count so that an expert
+// with many rows costs as few passes over its weights as possible.  The scale
+// words of the tiles are kept a second time in tile order (the reference layout
+// orders them by pool block).
+#ifndef GCMOE_PAIR_MIN_BLOCK_M
+#define GCMOE_PAIR_MIN_BLOCK_M 64
+#endif
+#ifndef GCMOE_PAIR_TILE_ROWS
+#define GCMOE_PAIR_TILE_ROWS 240
+#endif
+constexpr uint32_t kPairMinBlockM = GCMOE_PAIR_MIN_BLOCK_M;
+constexpr uint32_t kPairTileRows = GCMOE_PAIR_TILE_ROWS;
+constexpr uint32_t kSingleTileRows = 64;
+__host__ __device__ __forceinline__ bool pair_mode(uint32_t block_m) { return block_m >= kPairMinBlockM; }
 
 __host__ __device__ __forceinline__ uint32_t round_up_u32(uint32_t v, uint32_t m) {
     return (v + m - 1) / m * m;
+}
+// Rows per GEMM tile of an expert that received `n` rows on a rank whose pool
+// uses `block_m` (tile t covers rows [t * rows, ...)).  Depends only on values
+// every rank knows.
+__host__ __device__ __forceinline__ uint32_t expert_tile_rows(uint32_t block_m, uint32_t n) {
+    if (!pair_mode(block_m)) return kSingleTileRows;
+    if (n <= kPairTileRows) return n <= 16u ? 16u : round_up_u32(n, 16u);
+    const uint32_t tiles = (n + kPairTileRows - 1u) / kPairTileRows;
+    return round_up_u32((n + tiles - 1u) / tiles, 16u);
+}
+// Without room for the tile-ordered scale copy the tiles are the pool blocks.
+__host__ __device__ __forceinline__ uint32_t routed_tile_rows(uint32_t block_m, uint32_t n, bool tile_ordered) {
+    return tile_ordered ? expert_tile_rows(block_m, n) : block_m;
 }
 
 // Row, inside a 128-row-aligned scale block, of the block's u-th token: the

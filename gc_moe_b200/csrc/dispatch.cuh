@@ -55,9 +55,10 @@ struct DispatchParams {
     int* expert_block_start;      // [E_loc + 1] pool-block prefix (reference layout)
     int* expert_tile_start;       // [E_loc + 1] prefix of the GEMM tiles per expert
     int* expert_row_start;        // [E_loc] first pool row per expert
+    int* expert_sf_start;         // [E_loc] first row of the expert's scale chunks in the scale planes the GEMMs read
     uint32_t* call_info;          // [kCallInfoWords]
     int* shared_table;            // fused shared expert: {tokens, 0, row blocks}, or null
-    uint32_t* done_routed;        // per pool block: finished gate/up tiles, zeroed here for the GEMM launch
+    uint32_t* done_routed;        // per row tile: finished gate/up tiles, zeroed here for the GEMM launch
     uint32_t* done_shared;        // same for the shared expert's row blocks, or null
     int* stats;                   // optional cumulative per-expert counter (may be null)
     uint32_t* status;
@@ -68,13 +69,13 @@ struct DispatchParams {
     uint32_t private_sf_row;      // row offset, in each scale plane, of the tile-ordered scale copy (0 = none)
 };
 
-// Dynamic shared memory: six u32 per expert (own count, own routes before the
+// Dynamic shared memory: seven u32 per expert (own count, own routes before the
 // slice, total over sources, routes of lower sources, first pool block, first
-// GEMM tile), one block-M per rank, then the CTA's slice: expert id, pool row and
-// position inside the expert per route.
+// GEMM tile, first tile-ordered scale row), one block-M per rank, then the CTA's
+// slice: expert id, pool row and position inside the expert per route.
 __host__ __device__ inline uint32_t dispatch_smem_bytes(uint32_t num_experts, uint32_t num_ranks,
                                                         uint32_t slice) {
-    return (6 * num_experts + num_ranks + 8 + 3 * slice) * 4;
+    return (7 * num_experts + num_ranks + 8 + 3 * slice) * 4;
 }
 
 __global__ void __launch_bounds__(kDispatchThreads)
@@ -90,7 +91,8 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     uint32_t* const lower = total + E;          // [E] routes of source ranks below this one
     uint32_t* const first_block = lower + E;    // [E] first pool block of the expert at its owner
     uint32_t* const first_tile = first_block + E;   // [E] first GEMM tile of the expert at its owner
-    uint32_t* const bm_of = first_tile + E;     // [P] block-M of each rank's pool
+    uint32_t* const first_sf = first_tile + E;  // [E] first row of the expert's tile-ordered scale chunks at its owner
+    uint32_t* const bm_of = first_sf + E;       // [P] block-M of each rank's pool
     uint32_t* const misc = bm_of + P;           // [8] abort word, own pool blocks, own valid routes
     int* const slice_expert = reinterpret_cast<int*>(misc + 8);
     uint32_t* const slice_row = reinterpret_cast<uint32_t*>(slice_expert + slice);
@@ -180,36 +182,43 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     }
     __syncthreads();
 
-    // Pool-block prefix and GEMM-tile prefix of every owner's local experts
-    // (warp w: owners w, w+8, ...).  The GEMMs tile an expert's rows by
-    // gemm_tile_rows(BM) tokens rather than by pool blocks, so that an expert with
-    // many rows costs fewer passes over its weights.
+    // Pool-block prefix, GEMM-tile prefix and scale-chunk prefix of every owner's
+    // local experts (warp w: owners w, w+16, ...).  The GEMMs tile an expert's rows
+    // by expert_tile_rows(BM of the owner, rows of the expert) tokens rather than by
+    // pool blocks, and read the scale words of a tile from a chunk of its own
+    // (the tile's rows rounded up to 128) in the tile-ordered copy.
+    const bool tile_ordered = p.private_sf_row != 0u;
     for (uint32_t r = warp; r < P; r += kDispatchThreads / 32) {
         const uint32_t bm = bm_of[r], base = r * EL;
-        const uint32_t tn = p.private_sf_row ? gemm_tile_rows(bm, p.shared_table != nullptr) : bm;
         const uint32_t per_lane = (EL + 31) / 32;
-        uint32_t sum = 0, tsum = 0;
+        uint32_t sum = 0, tsum = 0, ssum = 0;
         for (uint32_t i = 0; i < per_lane; ++i) {
             const uint32_t l = lane * per_lane + i;
             if (l < EL) {
-                sum += (total[base + l] + bm - 1) / bm;
-                tsum += (total[base + l] + tn - 1) / tn;
+                const uint32_t n = total[base + l], tn = routed_tile_rows(bm, n, tile_ordered);
+                sum += (n + bm - 1) / bm;
+                tsum += (n + tn - 1) / tn;
+                ssum += (n + tn - 1) / tn * round_up_u32(tn, 128);
             }
         }
-        uint32_t incl = sum, tincl = tsum;
+        uint32_t incl = sum, tincl = tsum, sincl = ssum;
         for (uint32_t d = 1; d < 32; d <<= 1) {
             const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
             const uint32_t tv = __shfl_up_sync(0xffffffffu, tincl, d);
-            if (lane >= d) { incl += v; tincl += tv; }
+            const uint32_t sv = __shfl_up_sync(0xffffffffu, sincl, d);
+            if (lane >= d) { incl += v; tincl += tv; sincl += sv; }
         }
-        uint32_t run = incl - sum, trun = tincl - tsum;
+        uint32_t run = incl - sum, trun = tincl - tsum, srun = sincl - ssum;
         for (uint32_t i = 0; i < per_lane; ++i) {
             const uint32_t l = lane * per_lane + i;
             if (l < EL) {
+                const uint32_t n = total[base + l], tn = routed_tile_rows(bm, n, tile_ordered);
                 first_block[base + l] = run;
                 first_tile[base + l] = trun;
-                run += (total[base + l] + bm - 1) / bm;
-                trun += (total[base + l] + tn - 1) / tn;
+                first_sf[base + l] = srun;
+                run += (n + bm - 1) / bm;
+                trun += (n + tn - 1) / tn;
+                srun += (n + tn - 1) / tn * round_up_u32(tn, 128);
             }
         }
         if (r == p.rank && lane == 31) { misc[1] = incl; misc[3] = tincl; }   // pool blocks, GEMM tiles of this rank
@@ -222,15 +231,13 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     }
     __syncthreads();
 
-    // Tile counters of this call's row blocks start from zero.
-    for (uint32_t i = blockIdx.x * kDispatchThreads + tid; i <= misc[3]; i += gridDim.x * kDispatchThreads)
-        p.done_routed[i] = 0;
-    if (p.done_shared != nullptr)
-        for (uint32_t i = blockIdx.x * kDispatchThreads + tid; i <= (p.num_tokens + p.block_m - 1) / p.block_m;
-             i += gridDim.x * kDispatchThreads)
-            p.done_shared[i] = 0;
     const uint32_t first_local = p.rank * EL;
     if (blockIdx.x == 0) {
+        // Tile counters of this call's row tiles start from zero.
+        for (uint32_t i = tid; i <= misc[3]; i += kDispatchThreads) p.done_routed[i] = 0;
+        if (p.done_shared != nullptr)
+            for (uint32_t i = tid; i <= (p.num_tokens + p.block_m - 1) / p.block_m; i += kDispatchThreads)
+                p.done_shared[i] = 0;
         // ---- what this rank receives: the reference's count products and the
         // tables the GEMM kernels schedule from
         unsigned long long* recv = reinterpret_cast<unsigned long long*>(my_arena + p.off_recv_count) +
@@ -245,13 +252,16 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             p.expert_block_start[l] = static_cast<int>(first_block[first_local + l]);
             p.expert_tile_start[l] = static_cast<int>(first_tile[first_local + l]);
             p.expert_row_start[l] = static_cast<int>(first_block[first_local + l] * p.block_m);
+            // tiles that are the pool blocks read the scale words where the reference layout has them
+            p.expert_sf_start[l] = static_cast<int>(tile_ordered ? first_sf[first_local + l]
+                                                                 : first_block[first_local + l] * round_up_u32(p.block_m, 128));
             for (uint32_t s = 0; s < P; ++s)
                 recv[static_cast<size_t>(s) * EL + l] = P > 1 ? counts[static_cast<size_t>(s) * E + first_local + l] : n;
             // high word: number of source ranks that have reported
             recv_sum[l] = (static_cast<unsigned long long>(P) << 32) | n;
             if (p.stats != nullptr) p.stats[l] += static_cast<int>(n);
         }
-        if (P > 1) {
+        {
             // Counters of the NEXT call's generation start from zero; nobody can be
             // adding to them yet (a peer reaches its next call only after this
             // rank has finished the current one).
@@ -272,7 +282,17 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
                 p.shared_table[1] = 0;
                 p.shared_table[2] = static_cast<int>((p.num_tokens + p.block_m - 1) / p.block_m);
                 p.shared_table[3] = 0;     // the shared expert's rows start at token 0
+                p.shared_table[4] = 0;     // ... and so do its scale chunks
             }
+        }
+        // The GEMM launch of this call is already running (it was allowed to start when
+        // this kernel did): hand it the tables.  The barrier orders every thread's
+        // writes above before the release.
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.call_info + kCallTablesReady), "r"(epoch + 1u)
+                         : "memory");
         }
     }
 
@@ -348,21 +368,25 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         const uint32_t block = row / bm, u = row - block * bm;
         const uint32_t sf_row = block * sf_block + sf_row_in_block(u);
         uint32_t* sf_dst = reinterpret_cast<uint32_t*>(dst_arena + p.off_l1_acts_sf);
-        // second copy, ordered by GEMM tile, when the tiles are not the pool blocks
-        const uint32_t tn = p.private_sf_row ? gemm_tile_rows(bm, p.shared_table != nullptr) : bm;
+        // second copy, ordered by GEMM tile: the one the owner's GEMM launch reads
+        const uint32_t tn = routed_tile_rows(bm, total[e], tile_ordered);
         const uint32_t pos = slice_pos[a - lo];
-        const uint32_t tile_row = p.private_sf_row + (first_tile[e] + pos / tn) * round_up_u32(tn, 128) +
+        const uint32_t tile_row = p.private_sf_row + first_sf[e] + (pos / tn) * round_up_u32(tn, 128) +
                                   sf_row_in_block(pos % tn);
         for (uint32_t w = lane; w < sf_words; w += 32) {
             const uint32_t word = p.x_sf[static_cast<size_t>(t) * sf_words + w];
             sf_dst[static_cast<size_t>(w) * p.sf_ring + sf_row] = word;
-            if (tn != bm) sf_dst[static_cast<size_t>(w) * p.sf_ring + tile_row] = word;
+            if (tile_ordered) sf_dst[static_cast<size_t>(w) * p.sf_ring + tile_row] = word;
         }
-        if (P > 1) {
-            __syncwarp();
-            if (lane == 0)      // release, cumulative over the warp's stores ordered by __syncwarp
-                ptx::red_release_sys_add(reinterpret_cast<uint32_t*>(dst_arena + p.off_exchange + exchange::kRowsArrived) +
-                                             gen * kMaxLocalExperts + (e - owner * EL), 1u);
+        // Tell the owner's GEMM launch (which may already be running, on this GPU too)
+        // that one more row of the expert has landed: a release, cumulative over the
+        // warp's stores ordered by __syncwarp.
+        __syncwarp();
+        if (lane == 0) {
+            uint32_t* const arrived = reinterpret_cast<uint32_t*>(dst_arena + p.off_exchange + exchange::kRowsArrived) +
+                                      gen * kMaxLocalExperts + (e - owner * EL);
+            if (P > 1) ptx::red_release_sys_add(arrived, 1u);
+            else asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(arrived), "r"(1u) : "memory");
         }
     }
 }

@@ -56,7 +56,7 @@ static int get_encoder(EncodeTiledFn* fn) {
 
 static int encode_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank, uint64_t address,
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
-                      const char* what) {
+                      const char* what, bool swizzle128 = true) {
     EncodeTiledFn encode;
     if (int rc = get_encoder(&encode)) return rc;
     cuuint64_t gdims[5], gstrides[4];
@@ -64,7 +64,7 @@ static int encode_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank,
     for (uint32_t i = 0; i < rank; ++i) { gdims[i] = dims[i]; gbox[i] = box[i]; estr[i] = 1; }
     for (uint32_t i = 0; i + 1 < rank; ++i) gstrides[i] = strides_bytes[i];
     CUresult r = encode(map, type, rank, reinterpret_cast<void*>(address), gdims, gstrides, gbox, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(GCMOE_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, int(r));
@@ -88,6 +88,7 @@ struct Plan {
     CombineParams combine;
     uint32_t dispatch_grid = 1, dispatch_smem = 0;
     uint32_t gemm_grid = 1, gemm_smem = 0;
+    bool pair = false;            // the GEMM launch runs as CTA pairs (clusters of two, cta_group::2)
     uint32_t combine_grid = 1;
 };
 
@@ -136,9 +137,9 @@ extern "C" const char* gcmoe_last_error(void) { return g_error; }
 extern "C" size_t gcmoe_scratch_bytes(const gcmoe_problem* problem) {
     if (problem == nullptr || problem->num_ranks <= 0) return 0;
     const size_t local = size_t(problem->num_experts / problem->num_ranks);
-    // status | count | block prefix | tile prefix | row start | call info | shared table | tile counters
+    // status | count | block prefix | tile prefix | row start | scale start | call info | shared table | tile counters
     const size_t counters = size_t(problem->ring_tokens) / 16 + local + size_t(problem->capacity) / 16 + 4;
-    return round_up_u32(uint32_t(kStatusWords * 4 + (4 * local + 2) * 4 + kCallInfoWords * 4 + 4 * 4 + counters * 4), 256);
+    return round_up_u32(uint32_t(kStatusWords * 4 + (5 * local + 2) * 4 + kCallInfoWords * 4 + 8 * 4 + counters * 4), 256);
 }
 
 extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
@@ -175,8 +176,10 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         return fail(GCMOE_ERR_INVALID, "exchange block missing or too small for %d ranks x %d experts",
                     q.num_ranks, q.num_experts);
 
-    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     GCMOE_CUDA(cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
 
     gcmoe_plan* plan = new (std::nothrow) gcmoe_plan();
@@ -199,21 +202,29 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     const uint64_t arena = b.arena_base[q.rank];
     const uint64_t timeout_ns = uint64_t(q.timeout_ms > 0 ? q.timeout_ms : 2000) * 1000000ull;
 
-    // ---- scratch: status | expert_count[EL] | expert_block_start[EL + 1]
+    // ---- scratch: status | expert_count[EL] | block prefix[EL + 1] | tile prefix[EL + 1] | row start[EL] |
+    //      scale start[EL] | call info | shared table | tile counters
     plan->status = reinterpret_cast<uint32_t*>(b.scratch);
     int* expert_count = reinterpret_cast<int*>(b.scratch + kStatusWords * 4);
     int* expert_block_start = expert_count + EL;
     int* expert_tile_start = expert_block_start + EL + 1;
     int* expert_row_start = expert_tile_start + EL + 1;
-    uint32_t* call_info = reinterpret_cast<uint32_t*>(expert_row_start + EL);
+    int* expert_sf_start = expert_row_start + EL;
+    uint32_t* call_info = reinterpret_cast<uint32_t*>(expert_sf_start + EL);
 
-    // GEMM tiles need not be pool blocks (gemm_tile_rows); the
-    // scale words of such tiles are kept a second time, in tile order, in the upper half of every
-    // plane of the scale rings, which the reference layout never touches for block-M >= 16.
-    // Every rank must take the same decision: it depends on the buffer geometry only.
+    // GEMM tiles need not be pool blocks (expert_tile_rows); the scale words of the tiles are kept a
+    // second time, in tile order, in the upper half of every plane of the scale rings, which the
+    // reference layout never touches for block-M >= 16.  Every rank must take the same decision: it
+    // depends on the buffer geometry only.  Worst case of the copy: every tile of 121+ rows (or every
+    // single-tile expert) takes a 256-row chunk.
+    const uint32_t half_sf = (uint32_t(q.sf_ring_tokens) / 2) & ~127u;
     const uint32_t private_sf_row =
-        (uint64_t(q.ring_tokens) / 64 + EL + 1) * 128 <= uint64_t(q.sf_ring_tokens) / 2 ? uint32_t(q.sf_ring_tokens) / 2 : 0u;
-    const uint32_t tn = private_sf_row ? gemm_tile_rows(bm, q.num_shared_experts > 0) : bm;   // rows per GEMM tile on this rank
+        (uint64_t(q.ring_tokens) / 120 + EL + 1) * 256 <= uint64_t(half_sf) ? half_sf : 0u;
+    const bool tile_ordered = private_sf_row != 0u;
+    const bool pair = pair_mode(bm);
+    plan->pair = pair;
+    // largest tile of the launch: accumulator stride, rows of an activation stage
+    const uint32_t tn = tile_ordered ? (pair ? kPairTileRows : (bm > kSingleTileRows ? bm : kSingleTileRows)) : bm;
     const uint32_t sftn = round_up_u32(tn, 128);
 
     // ---- dispatch
@@ -239,6 +250,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     d.expert_block_start = expert_block_start;
     d.expert_tile_start = expert_tile_start;
     d.expert_row_start = expert_row_start;
+    d.expert_sf_start = expert_sf_start;
     d.private_sf_row = private_sf_row;
     d.stats = reinterpret_cast<int*>(b.stats);
     d.status = plan->status;
@@ -257,13 +269,13 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
 
     // ---- the two grouped GEMMs (each: shared-expert segment first, then routed)
     const uint32_t S = q.num_shared_experts, IS = S * I;
-    const uint32_t table_words = 2 * ((3 * EL + 1) + (S ? 4 : 0));   // up and down segments each hold a copy
-    const uint32_t stages = gemm_pick_stages(tn, sftn, table_words);
+    const uint32_t table_words = 2 * ((4 * EL + 1) + (S ? 5 : 0));   // up and down segments each hold a copy
+    const uint32_t stages = gemm_pick_stages(tn, sftn, table_words, pair);
     if (stages < 2) return bail(fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm));
-    plan->gemm_smem = gemm_smem_layout(stages, tn, sftn, table_words).total + 1024;
+    plan->gemm_smem = gemm_smem_layout(stages, tn, sftn, table_words, pair).total + 1024;
     // Two accumulator stages (epilogue overlaps the next tile) while they fit TMEM.
-    const uint32_t acc_stages = gemm_tmem_columns(tn, sftn, 2) <= 512 ? 2u : 1u;
-    if (gemm_tmem_columns(tn, sftn, acc_stages) > 512)
+    const uint32_t acc_stages = gemm_tmem_columns(tn, sftn, 2, pair) <= 512 ? 2u : 1u;
+    if (gemm_tmem_columns(tn, sftn, acc_stages, pair) > 512)
         return bail(fail(GCMOE_ERR_UNSUPPORTED, "TMEM budget exceeded"));
 
     auto fill_common = [&](GemmParams& g) {
@@ -275,7 +287,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.stages = stages;
         g.acc_stages = acc_stages;
         g.table_words = table_words;
-        g.tmem_cols = pow2_at_least(gemm_tmem_columns(tn, sftn, acc_stages));
+        g.tmem_cols = pow2_at_least(gemm_tmem_columns(tn, sftn, acc_stages, pair));
         g.clamp = q.clamp;
         g.has_clamp = q.has_clamp != 0;
         g.fast_math = q.fast_math != 0;
@@ -285,6 +297,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.rank = q.rank;
         g.num_ranks = P;
         g.call_info = call_info;
+        g.epoch_word = reinterpret_cast<const uint32_t*>(arena + b.off_recv_parity);
         g.tile_cursor = call_info + kCallTileCursor;
         g.rows_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kRowsArrived);
         g.failed = reinterpret_cast<uint32_t*>(arena + b.off_exchange + exchange::kFailed);
@@ -293,55 +306,84 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
             g.combine_base[r] = b.arena_base[r] + b.off_combine_tokens;
         }
     };
+    // Activation boxes of a few heights: a tile fetches the smallest one that holds its rows
+    // (a CTA of a pair stages half of the tile's rows).
+    auto activation_maps = [&](GemmSegment& sg, uint64_t acts, uint32_t k, uint64_t rows, uint32_t max_rows,
+                               const char* what) -> int {
+        const uint32_t top = pair ? max_rows / 2 : max_rows;
+        const uint32_t heights[kMaxActMaps] = {8, 16, 32, 48, 64, 96, 112, 120};
+        const uint64_t adims[2] = {k, rows};
+        const uint64_t astr[1] = {k};
+        sg.num_act_maps = 0;
+        for (int i = 0; i < kMaxActMaps; ++i) {
+            uint32_t h = heights[i];
+            if (!pair && h < 16) continue;
+            if (h >= top || i == kMaxActMaps - 1) h = top;
+            const uint32_t abox[2] = {128, h};
+            if (int rc = encode_map(&sg.tm_act[sg.num_act_maps], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr,
+                                    abox, what))
+                return rc;
+            sg.act_box_rows[sg.num_act_maps++] = h;
+            if (h == top) break;
+        }
+        return GCMOE_OK;
+    };
+    // Scale words through tensor maps (CTA pairs only: their loads report to the leader's barrier).
+    auto scale_maps = [&](GemmSegment& sg, uint64_t acts_sf, uint64_t act_sf_rows, uint64_t act_sf_stride,
+                          uint32_t k_blocks, uint64_t w_sf, uint64_t w_sf_stride, uint64_t w_sf_planes,
+                          const char* what) -> int {
+        if (!pair) return GCMOE_OK;
+        const uint32_t box[2] = {128, 1};
+        const uint64_t adims[2] = {act_sf_rows, k_blocks}, astr[1] = {act_sf_stride * 4};
+        if (int rc = encode_map(&sg.tm_act_sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, acts_sf, adims, astr, box, what, false))
+            return rc;
+        const uint64_t wdims[2] = {w_sf_stride, w_sf_planes}, wstr[1] = {w_sf_stride * 4};
+        return encode_map(&sg.tm_w_sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w_sf, wdims, wstr, box, what, false);
+    };
     // Routed experts: FP4 weights [EL][K/128][rows][64 B], pool rows as activations.
     auto routed_segment = [&](GemmSegment& sg, uint64_t acts, uint64_t acts_sf, uint32_t k, uint64_t weights,
                               uint64_t w_sf, uint64_t w_sf_stride, uint32_t w_rows, const char* what) -> int {
         sg.tile_start = expert_tile_start;
         sg.count = expert_count;
         sg.row_start = expert_row_start;
+        sg.sf_start = expert_sf_start;
         sg.experts = EL;
-        sg.tile_rows = tn;
-        sg.narrow_rows = bm < tn ? bm : tn;   // tiles with at most this many rows fetch the smaller box
-        sg.sf_chunk_rows = sftn;
+        sg.tile_rows = tile_ordered ? 0u : bm;      // 0: per expert, from its row count
         sg.ref_block_m = bm;
-        sg.out_sf_private = tn != bm ? private_sf_row : 0u;
+        sg.out_sf_private = private_sf_row;
         sg.w_rows = w_rows;
         sg.k_blocks = k / 128;
         sg.n_tiles = w_rows / kTileRows;
         sg.weight_format = 5;
         sg.weight_tx_bytes = kTileRows * 128 / 2;
         sg.w_sf_kblocks = 1;
-        // tiles that are not pool blocks read the tile-ordered scale copy
-        sg.act_sf = reinterpret_cast<const uint32_t*>(acts_sf) + (tn != bm ? private_sf_row : 0u);
+        // the tile-ordered scale copy when there is one, else the reference layout (tiles = pool blocks)
+        sg.act_sf = reinterpret_cast<const uint32_t*>(acts_sf) + private_sf_row;
         sg.act_sf_stride = q.sf_ring_tokens;
         sg.w_sf = reinterpret_cast<const uint32_t*>(w_sf);
         sg.w_sf_stride = uint32_t(w_sf_stride);
-        const uint64_t adims[2] = {k, uint64_t(q.ring_tokens)};
-        const uint64_t astr[1] = {k};
-        const uint32_t abox[2] = {128, tn}, nbox[2] = {128, bm < tn ? bm : tn};
-        if (int rc = encode_map(&sg.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
-            return rc;
-        if (int rc = encode_map(&sg.tm_act_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, nbox, what))
+        if (int rc = activation_maps(sg, acts, k, uint64_t(q.ring_tokens), tn, what)) return rc;
+        if (int rc = scale_maps(sg, acts_sf + uint64_t(private_sf_row) * 4, uint64_t(q.sf_ring_tokens) - private_sf_row,
+                                uint64_t(q.sf_ring_tokens), k / 128, w_sf, w_sf_stride, uint64_t(EL) * (k / 128), what))
             return rc;
         // 128-element (64-byte) rows of one K128 tile are adjacent, so a 128 x 256
         // box is one contiguous 16 KiB range in HBM.
         const uint64_t wdims[4] = {128, w_rows, k / 128, EL};
         const uint64_t wstr[3] = {64, uint64_t(w_rows) * 64, uint64_t(w_rows) * 64 * (k / 128)};
-        const uint32_t wbox[4] = {128, kTileRows, 1, 1};
+        const uint32_t wbox[4] = {128, uint32_t(pair ? kHalfRows : kTileRows), 1, 1};
         return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, weights, wdims, wstr, wbox, what);
     };
     // Shared expert: FP8 weights [K/128][rows][128 B], this rank's own tokens as rows.
-    int* shared_table = reinterpret_cast<int*>(call_info + kCallInfoWords);   // count, start[0], start[1]
+    int* shared_table = reinterpret_cast<int*>(call_info + kCallInfoWords);   // count, start[0], start[1], row start, scale start
     auto shared_segment = [&](GemmSegment& sg, uint64_t acts, uint64_t acts_sf, uint32_t k, uint64_t weights,
                               uint64_t w_sf, uint64_t w_sf_stride, uint32_t w_rows, const char* what) -> int {
         sg.shared = 1;
         sg.count = shared_table;
         sg.tile_start = shared_table + 1;
         sg.row_start = shared_table + 3;
+        sg.sf_start = shared_table + 4;
         sg.experts = 1;
         sg.tile_rows = bm;            // the caller stages the scales in block-M order
-        sg.narrow_rows = bm;
-        sg.sf_chunk_rows = sfbm;
         sg.ref_block_m = bm;
         sg.w_rows = w_rows;
         sg.k_blocks = k / 128;
@@ -353,23 +395,23 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         sg.act_sf_stride = uint32_t(b.shared_sf_rows);
         sg.w_sf = reinterpret_cast<const uint32_t*>(w_sf);
         sg.w_sf_stride = uint32_t(w_sf_stride);
-        const uint64_t adims[2] = {k, uint64_t(q.capacity)};
-        const uint64_t astr[1] = {k};
-        const uint32_t abox[2] = {128, bm};
-        if (int rc = encode_map(&sg.tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what))
+        if (int rc = activation_maps(sg, acts, k, uint64_t(q.capacity), bm, what)) return rc;
+        const uint32_t planes = (k / 128 + sg.w_sf_kblocks - 1) / sg.w_sf_kblocks;
+        if (int rc = scale_maps(sg, acts_sf, b.shared_sf_rows, b.shared_sf_rows, k / 128, w_sf, w_sf_stride, planes, what))
             return rc;
-        sg.tm_act_narrow = sg.tm_act;
         const uint64_t wdims[3] = {128, w_rows, k / 128};
         const uint64_t wstr[2] = {128, uint64_t(w_rows) * 128};
-        const uint32_t wbox[3] = {128, kTileRows, 1};
+        const uint32_t wbox[3] = {128, uint32_t(pair ? kHalfRows : kTileRows), 1};
         return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, weights, wdims, wstr, wbox, what);
     };
 
-    // Per-row-block counters of finished up tiles (zeroed by the dispatch kernel).
-    uint32_t* done_routed = reinterpret_cast<uint32_t*>(shared_table + 4);
+    // Per-row-tile counters of finished up tiles (zeroed by the dispatch kernel).
+    uint32_t* done_routed = reinterpret_cast<uint32_t*>(shared_table + 8);
     uint32_t* done_shared = done_routed + q.ring_tokens / 16 + EL + 1;
     d.done_routed = done_routed;
     d.done_shared = S ? done_shared : nullptr;
+    // a CTA of a pair finishes one half of an up tile
+    const uint32_t done_per_tile = pair ? 2u : 1u;
 
     GemmSegment shared_up, shared_down, routed_up, routed_down;
     memset(&shared_up, 0, sizeof(GemmSegment));
@@ -389,7 +431,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
                                     b.sw2, b.sw2_sf, b.sw2_sf_stride, H, "shared down GEMM")) return bail(rc);
         shared_down.kind = kSegDown;
         shared_down.block_done = done_shared;
-        shared_down.done_target = shared_up.n_tiles;
+        shared_down.done_target = shared_up.n_tiles * done_per_tile;
     }
     if (int rc = routed_segment(routed_up, arena + b.off_l1_acts, arena + b.off_l1_acts_sf, H, b.w1, b.w1_sf,
                                 b.w1_sf_stride, 2 * I, "gate/up GEMM")) return bail(rc);
@@ -405,7 +447,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     routed_down.kind = kSegDown;
     routed_down.metadata = reinterpret_cast<const uint32_t*>(arena + b.off_metadata);
     routed_down.block_done = done_routed;
-    routed_down.done_target = routed_up.n_tiles;
+    routed_down.done_target = routed_up.n_tiles * done_per_tile;
 
     fill_common(plan->up);
     fill_common(plan->down);
@@ -428,9 +470,32 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     const uint64_t shared_blocks = S ? (uint64_t(q.num_tokens) + bm - 1) / bm : 0;
     {
         // With several ranks the pool depends on what the other ranks send.
-        const uint64_t tiles = P > 1 ? uint64_t(plan->num_sms)
+        uint64_t tiles = P > 1 ? uint64_t(plan->num_sms)
             : max_blocks * routed_up.n_tiles + (S ? shared_blocks * shared_up.n_tiles : 0);
-        plan->gemm_grid = uint32_t(tiles < uint64_t(plan->num_sms) ? tiles : uint64_t(plan->num_sms));
+        if (pair) tiles *= 2;        // two CTAs per tile
+        uint32_t grid = uint32_t(tiles < uint64_t(plan->num_sms) ? tiles : uint64_t(plan->num_sms));
+        if (pair) {
+            // Every CTA of the launch must be resident (down tiles wait for up tiles of running
+            // CTAs): no more clusters than the device can hold at once.
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(plan->num_sms & ~1);
+            cfg.blockDim = dim3(kGemmThreads);
+            cfg.dynamicSmemBytes = plan->gemm_smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            cudaError_t oe = cudaOccupancyMaxActiveClusters(&clusters, grouped_gemm_kernel<false, true>, &cfg);
+            if (oe != cudaSuccess || clusters < 1)
+                return bail(fail(GCMOE_ERR_CUDA, "cudaOccupancyMaxActiveClusters: %s (%d clusters)",
+                                 cudaGetErrorString(oe), clusters));
+            grid &= ~1u;
+            if (grid < 2) grid = 2;
+            if (grid > uint32_t(clusters) * 2) grid = uint32_t(clusters) * 2;
+        }
+        plan->gemm_grid = grid;
     }
 
     // ---- combine
@@ -448,7 +513,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     c.failed = reinterpret_cast<uint32_t*>(arena + b.off_exchange + exchange::kFailed);
     c.status = plan->status;
     c.timeout_ns = timeout_ns;
-    c.tiles_per_row = H / kTileRows;
+    c.halves_per_row = H / kHalfRows;
     const uint64_t cvecs = uint64_t(q.num_tokens) * (H / 8);
     uint64_t cgrid = (cvecs + kCombineThreads - 1) / kCombineThreads;
     const uint64_t cmax = uint64_t(plan->num_sms) * 8;
@@ -469,21 +534,44 @@ extern "C" int gcmoe_kernels_per_launch(const gcmoe_plan* plan) {
 
 // Launch with programmatic stream serialization: the kernel may start while
 // its predecessor in the stream is still running and orders itself with
-// griddepcontrol.wait, so its prologue overlaps the predecessor's tail.
+// griddepcontrol.wait (or, for the GEMM launch, with the flags the dispatch
+// kernel raises), so it overlaps the predecessor.  `cluster` > 1 launches
+// thread-block clusters of that many CTAs.
 template <typename Params>
 static cudaError_t launch_dependent(void (*kernel)(Params), uint32_t grid, uint32_t block, uint32_t smem,
-                                    cudaStream_t stream, const Params& params, bool dependent) {
+                                    cudaStream_t stream, const Params& params, bool dependent,
+                                    uint32_t cluster = 1) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(block);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (dependent) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = dependent ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, params);
+}
+
+template <bool kRaw>
+static cudaError_t launch_gemm(const gcmoe::Plan* plan, const GemmParams& g, cudaStream_t s, bool dependent) {
+    if (plan->pair)
+        return launch_dependent(grouped_gemm_kernel<kRaw, true>, plan->gemm_grid, kGemmThreads, plan->gemm_smem, s, g,
+                                dependent, 2);
+    return launch_dependent(grouped_gemm_kernel<kRaw, false>, plan->gemm_grid, kGemmThreads, plan->gemm_smem, s, g,
+                            dependent);
 }
 
 extern "C" int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned mask, void* cuda_stream) {
@@ -498,9 +586,11 @@ extern "C" int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned mask, void* cuda_
     }
     if (mask & 6u) {
         // both GEMMs of the layer are one launch; either one alone is for tests and timing
-        const GemmParams& g = (mask & 6u) == 6u ? plan->fused : (mask & 2u) ? plan->up : plan->down;
-        GCMOE_CUDA(launch_dependent(grouped_gemm_kernel<false>, plan->gemm_grid, kGemmThreads, plan->gemm_smem, s, g,
-                                    chained));
+        GemmParams g = (mask & 6u) == 6u ? plan->fused : (mask & 2u) ? plan->up : plan->down;
+        // Launched together with the call's dispatch kernel the GEMMs start while it runs and
+        // wait for its tables; launched alone they find the tables of the last call in place.
+        g.wait_tables = chained ? 1u : 0u;
+        GCMOE_CUDA(launch_gemm<false>(plan, g, s, chained));
         chained = true;
     } else chained = false;
     if (mask & 8u)
@@ -524,17 +614,6 @@ extern "C" int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* 
                     words[kStatusCode], words[kStatusKernel], words[kStatusSite], words[kStatusBlock],
                     words[kStatusObserved], words[kStatusExpected]);
     return GCMOE_OK;
-}
-
-extern "C" int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cuda_stream) {
-    if (plan == nullptr || out == 0 || which < 0 || which > 2) return fail(GCMOE_ERR_INVALID, "bad argument");
-    GemmParams g = which == 0 ? plan->up : which == 1 ? plan->down : plan->fused;
-    g.timing = reinterpret_cast<unsigned long long*>(out);
-    const uint32_t grid = plan->gemm_grid;
-    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-    grouped_gemm_kernel<false><<<grid, kGemmThreads, plan->gemm_smem, s>>>(g);
-    GCMOE_CUDA(cudaGetLastError());
-    return int(grid);
 }
 
 // A wait on a word nothing ever sets, with a short limit: exercises the timeout
@@ -608,8 +687,8 @@ extern "C" int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cud
     g.seg[0] = plan->up.seg[plan->up.num_segments - 1];   // the routed gate/up segment alone
     g.num_segments = 1;
     g.raw_out = reinterpret_cast<float*>(out);
-    grouped_gemm_kernel<true><<<plan->gemm_grid, kGemmThreads, plan->gemm_smem,
-                                    static_cast<cudaStream_t>(cuda_stream)>>>(g);
+    g.wait_tables = 0;
+    GCMOE_CUDA(launch_gemm<true>(plan, g, static_cast<cudaStream_t>(cuda_stream), false));
     GCMOE_CUDA(cudaGetLastError());
     return GCMOE_OK;
 }
@@ -629,12 +708,13 @@ namespace gcmoe {
 
 constexpr int kStaticMaxLocalExperts = 128;
 constexpr size_t kStaticScratchBytes = 65536;  // status, counts, prefix for 128 local experts, tile counters of ~16000 row blocks
-static_assert(kStaticScratchBytes >= kStatusWords * 4 + (4 * kStaticMaxLocalExperts + 2) * 4 + kCallInfoWords * 4 + 16, "static scratch too small");
+static_assert(kStaticScratchBytes >= kStatusWords * 4 + (5 * kStaticMaxLocalExperts + 2) * 4 + kCallInfoWords * 4 + 32, "static scratch too small");
 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
 static void* g_static_scratch_address[kMaxDevices] = {};
+static const uint32_t* g_static_last_failed_word[kMaxDevices] = {};   // sticky failure word of the last call's workspace
 static std::mutex g_static_scratch_mutex;
 
 // Device address of g_static_scratch on the current device.  In host code the
@@ -663,10 +743,15 @@ extern "C" int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const g
     if (problem->num_ranks <= 0 || problem->num_experts <= 0)
         return fail(GCMOE_ERR_INVALID, "invalid rank/expert configuration");
     const int local = problem->num_experts / problem->num_ranks;
-    if (local > kStaticMaxLocalExperts || gcmoe_scratch_bytes(problem) > kStaticScratchBytes)
+    if (local > kStaticMaxLocalExperts)
         return fail(GCMOE_ERR_UNSUPPORTED,
                     "%d local experts exceed the %d the built-in scratch holds; use gcmoe_plan_create "
                     "with caller-provided scratch", local, kStaticMaxLocalExperts);
+    if (gcmoe_scratch_bytes(problem) > kStaticScratchBytes)
+        return fail(GCMOE_ERR_UNSUPPORTED,
+                    "the tile counters of a ring of %d rows and a capacity of %d tokens need %zu bytes of scratch, "
+                    "more than the %zu the built-in scratch holds; use gcmoe_plan_create with caller-provided scratch",
+                    problem->ring_tokens, problem->capacity, gcmoe_scratch_bytes(problem), kStaticScratchBytes);
     void* scratch = nullptr;
     if (int rc = static_scratch_address(&scratch)) return rc;
     gcmoe_buffers with_scratch = *buffers;
@@ -675,12 +760,22 @@ extern "C" int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const g
     gcmoe_plan* plan = nullptr;
     if (int rc = gcmoe_plan_create(problem, &with_scratch, &plan)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
-    // The array keeps what the previous call left: the status words must start at zero,
-    // and so must the GEMM launch's tile cursor, whose place depends on the geometry.
+    // The array keeps what the previous call left: the status words must start at zero, and so
+    // must the call-info words (the tables-ready word the GEMM launch waits for, its tile
+    // cursor), whose place depends on the geometry.  The rest is rewritten by the dispatch kernel.
     cudaError_t err = cudaMemsetAsync(scratch, 0, kStatusWords * 4, s);
-    if (err == cudaSuccess) err = cudaMemsetAsync(plan->fused.tile_cursor, 0, sizeof(uint32_t), s);
+    if (err == cudaSuccess)
+        err = cudaMemsetAsync(const_cast<uint32_t*>(plan->fused.call_info), 0, kCallInfoWords * sizeof(uint32_t), s);
     int rc = err == cudaSuccess ? gcmoe_launch(plan, cuda_stream)
                                 : fail(GCMOE_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(err));
+    if (rc == GCMOE_OK) {
+        // A workspace on which a wait has given up stays failed: its kernels return at once and write
+        // nothing.  Remember where its sticky word lives so that the status query reports that too.
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        int device = 0;
+        if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < kMaxDevices)
+            g_static_last_failed_word[device] = plan->fused.failed;
+    }
     gcmoe_plan_destroy(plan);   // host object only; the enqueued kernels carry their parameters by value
     return rc;
 }
@@ -691,9 +786,22 @@ extern "C" int gcmoe_static_scratch_status(void* cuda_stream, uint32_t* words) {
     if (int rc = static_scratch_address(&scratch)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
     GCMOE_CUDA(cudaMemcpyAsync(words, scratch, kStatusWords * 4, cudaMemcpyDeviceToHost, s));
+    const uint32_t* failed_word = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+        int device = 0;
+        if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < kMaxDevices)
+            failed_word = g_static_last_failed_word[device];
+    }
+    uint32_t workspace_failed = 0;
+    if (failed_word != nullptr)
+        GCMOE_CUDA(cudaMemcpyAsync(&workspace_failed, failed_word, sizeof(uint32_t), cudaMemcpyDeviceToHost, s));
     GCMOE_CUDA(cudaStreamSynchronize(s));
     if (words[kStatusCode] != 0)
         return fail(GCMOE_ERR_DEVICE, "device wait gave up: code %u kernel %u site %u block %u",
                     words[kStatusCode], words[kStatusKernel], words[kStatusSite], words[kStatusBlock]);
+    if (workspace_failed != 0)
+        return fail(GCMOE_ERR_DEVICE, "device wait gave up in an earlier call on this workspace: its kernels "
+                                      "return at once until the workspace is re-created");
     return GCMOE_OK;
 }

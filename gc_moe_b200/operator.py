@@ -24,12 +24,19 @@ _PLAN_CACHE_LIMIT = 64
 
 
 class _Plan:
-    """A native plan plus everything whose lifetime it depends on."""
+    """A native plan plus everything whose lifetime it depends on.
+
+    ``pinned`` is set once the plan has been created or launched while its
+    stream was being captured: a CUDA graph then holds the addresses of the
+    plan's scratch block in its kernel parameters, so the plan (and with it the
+    scratch) must stay alive for as long as the workspace does.
+    """
 
     def __init__(self, handle, scratch, keepalive):
         self.handle = handle
         self.scratch = scratch
         self.keepalive = keepalive
+        self.pinned = False
 
 
 def _timeout_ms() -> int:
@@ -109,21 +116,41 @@ def _plan_key(config: ValidatedCall, y, l1_weights, l2_weights, shared_l1, share
             stats.data_ptr() if stats is not None else 0, _timeout_ms())
 
 
+def _capturing() -> bool:
+    return torch.cuda.is_current_stream_capturing()
+
+
 def get_plan(config, y, l1_weights, l2_weights, call_buffer, shared_l1, shared_l2, stats) -> _Plan:
     """Plan for this exact call signature, cached on the workspace.  Cached
     plans keep their tensors alive, as the reference's launch cache does for
-    graphs that captured them (jit_kernels/impls/sm100_fp8_fp4_gc_moe.py:206-209)."""
+    graphs that captured them (jit_kernels/impls/sm100_fp8_fp4_gc_moe.py:206-209:
+    "Entries remain alive; no cache clear may release in-flight graph
+    resources").  Only plans no graph can refer to are ever evicted: the oldest
+    one that was never used under stream capture, and only outside capture."""
     owner = getattr(call_buffer, '_base', call_buffer)
     key = _plan_key(config, y, l1_weights, l2_weights, shared_l1, shared_l2, stats)
+    capturing = _capturing()
     plan = owner._plans.get(key)
     if plan is None:
-        if len(owner._plans) >= _PLAN_CACHE_LIMIT and not torch.cuda.is_current_stream_capturing():
-            oldest = next(iter(owner._plans))
-            release_plan(owner._plans.pop(oldest))
+        if len(owner._plans) >= _PLAN_CACHE_LIMIT and not capturing:
+            victim = next((k for k, cached in owner._plans.items() if not cached.pinned), None)
+            if victim is not None:
+                retire_plan(owner, owner._plans.pop(victim))
         plan = _build_plan(config, y, l1_weights, l2_weights, call_buffer, shared_l1,
                            shared_l2, stats)
         owner._plans[key] = plan
+    if capturing:
+        plan.pinned = True
     return plan
+
+
+def retire_plan(owner, plan: _Plan) -> None:
+    """Drop an evicted plan.  Its kernels may still be running and its status
+    block may hold a failure nobody has read yet: the scratch block is parked on
+    the workspace until the next ``raise_on_device_error`` has looked at it."""
+    owner._retired_scratch.append(plan.scratch)
+    del owner._retired_scratch[:-256]       # bounded: beyond that the oldest blocks go back to the allocator
+    release_plan(plan)
 
 
 def release_plan(plan: _Plan) -> None:
@@ -136,6 +163,14 @@ def check_plan_status(plan: _Plan) -> None:
     words = (ctypes.c_uint32 * _native.STATUS_WORDS)()
     stream = torch.cuda.current_stream().cuda_stream
     _native.raise_for(_native.library().gcmoe_status_read(plan.handle, ctypes.c_void_p(stream), words))
+
+
+def check_retired_status(scratch: torch.Tensor) -> None:
+    """Status words of a plan that has been evicted (the block starts with them)."""
+    words = scratch[:_native.STATUS_WORDS * 4].view(torch.int32).tolist()
+    if words[0] != 0:
+        raise RuntimeError(f'device wait gave up: code {words[0]} kernel {words[1]} site {words[2]} '
+                           f'block {words[3]} observed {words[4]} expected {words[5]}')
 
 
 def _launch(config, y, l1_weights, l2_weights, call_buffer, shared_l1, shared_l2, stats) -> None:

@@ -121,8 +121,11 @@ int gcmoe_launch(gcmoe_plan* plan, void* cuda_stream);
 
 /* Enqueue only the kernels selected by `kernel_mask` (bit 0 dispatch, bit 1
  * gate/up tiles, bit 2 down tiles, bit 3 combine); bits 1 and 2 together are
- * the layer's single GEMM launch, either alone runs only those tiles.  Used by
- * the parity tests and for per-kernel timing. */
+ * the layer's single GEMM launch, either alone runs only those tiles.  Kernels
+ * enqueued by one call may overlap (the GEMM launch starts while the dispatch
+ * kernel is still pushing rows); kernels enqueued by separate calls run one
+ * after the other, which is how per-kernel times are taken.  A GEMM launch
+ * without its dispatch kernel reuses the tables of the last complete call. */
 int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned kernel_mask, void* cuda_stream);
 
 /* Number of kernels gcmoe_launch enqueues per call. */
@@ -134,9 +137,11 @@ int gcmoe_kernels_per_launch(const gcmoe_plan* plan);
  * (gc_moe/comm/gc_barrier.py:44-80). */
 int gcmoe_status_read(gcmoe_plan* plan, void* cuda_stream, uint32_t* words);
 
-/* Raw grouped GEMM over an already dispatched pool: FP32 accumulators of
- * W1 x pool rows to `out` ([pool rows][2I] floats).  Test hook for the MMA,
- * descriptor and scale plumbing. */
+/* Raw grouped GEMM over the pool of the last complete call: FP32 accumulators
+ * of W1 x pool rows to `out` ([pool rows][2I] floats, row r of the pool at
+ * out[r * 2I], weight rows in the transformed (gate/up interleaved) order).
+ * Test hook for the MMA, descriptor and scale plumbing of both tile regimes
+ * (gc_moe/mma/sm100.py:22-254 is what it stands in for). */
 int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream);
 
 /* Enqueue a one-thread kernel that waits, for at most `timeout_us`, on a word
@@ -145,16 +150,6 @@ int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream);
  * failure detection on a healthy GPU; the reference's counterpart is the
  * timeout path of comm/gc_barrier.py:44-80, which traps instead. */
 int gcmoe_debug_expire_wait(gcmoe_plan* plan, unsigned timeout_us, void* cuda_stream);
-
-/* Run the grouped GEMM launch (which = 0 gate/up tiles only, 1 down tiles only,
- * 2 both as in a layer call) with per-role
- * cycle counters written to `out`: uint64 [grid][6][4]; entries 0-4 = {cycles
- * in the role loop, cycles in its first wait, cycles in its second wait, tiles}
- * of the weight producer, activation producer, MMA warp 0, MMA warp 1 and
- * epilogue; entry 5 = the CTA's global-timer nanoseconds at kernel entry, at
- * the start of the roles and at exit.  Returns the grid size.  Tuning aid; no counterpart in the
- * reference, which has no tracing (only printf on timeouts). */
-int gcmoe_debug_role_timing(gcmoe_plan* plan, int which, uint64_t out, void* cuda_stream);
 
 /* Inputs of gcmoe_stage_inputs: device addresses and element counts. */
 typedef struct gcmoe_stage_args {
@@ -193,23 +188,32 @@ int gcmoe_stage_inputs(const gcmoe_stage_args* args, void* cuda_stream);
  * scratch block gcmoe_plan_create asks for.  The kernels' scratch (status
  * words, per-expert token counts, pool-block prefix, per-block tile counters)
  * lives in a fixed 64 KiB device array inside the library instead, enough for
- * 128 local experts and about 16000 row blocks; larger problems are rejected
- * with GCMOE_ERR_UNSUPPORTED.
+ * 128 local experts and about 15000 row-tile counters (ring_tokens / 16 +
+ * capacity / 16 of them are reserved); a problem beyond either limit is
+ * rejected with GCMOE_ERR_UNSUPPORTED and a message that names the limit.
  * `buffers->scratch` is ignored; the arena, weights and y are still the
  * caller's.  No cudaMalloc / cudaFree or any other allocating device routine
  * is called; one small host object lives for the duration of the call.
  *
+ * Host cost: unlike gcmoe_launch, which reuses a plan, every call here checks
+ * the geometry again and encodes the layer's tensor maps again on the host
+ * (tens of microseconds) before it enqueues anything.
+ *
  * The first call on a device looks up the array's device address; make that
  * first call before starting any stream capture on that device.  All calls on
- * a device share the one array: its status words and the GEMM launch's tile
- * cursor are cleared on the stream before the kernels, the rest is rewritten
- * by the dispatch kernel, and two
+ * a device share the one array: its status words and call-info words (the
+ * tables-ready word, the GEMM launch's tile cursor) are cleared on the stream
+ * before the kernels, the rest is rewritten by the dispatch kernel, and two
  * calls whose kernels overlap on the GPU (different streams) race on it. */
 int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const gcmoe_buffers* buffers,
                                 void* cuda_stream);
 
 /* Status words of the built-in scratch after synchronising `cuda_stream`
- * (same meaning as gcmoe_status_read). */
+ * (same meaning as gcmoe_status_read).  Each call clears the status words, so
+ * a wait that gave up is in them only until the next call; the failure stays
+ * visible all the same, because this query also reads the sticky failure word
+ * of the workspace the last call used and returns GCMOE_ERR_DEVICE while it
+ * is set (the kernels of such a workspace return at once and leave y alone). */
 int gcmoe_static_scratch_status(void* cuda_stream, uint32_t* words);
 
 #ifdef __cplusplus

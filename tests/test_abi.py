@@ -88,3 +88,24 @@ def test_stage_inputs_struct_and_argument_errors_need_no_gpu(lib, tmp_path):
         assert lib.gcmoe_stage_inputs(ctypes.byref(args), None) == _native.ERR_INVALID, bad
     # no tokens: nothing to do, nothing launched
     assert lib.gcmoe_stage_inputs(ctypes.byref(_native.StageArgs(**{**good, 'num_tokens': 0})), None) == 0
+
+
+def test_static_scratch_limits_are_checked_before_any_cuda_call(lib):
+    """The entry point for callers that cannot allocate holds its scratch in a fixed
+    64 KiB array: both ways of outgrowing it are refused with a message that names
+    the limit that was exceeded (no GPU needed: the checks come first)."""
+    bufs = _native.Buffers()
+    many_experts = _native.Problem(num_ranks=1, rank=0, num_experts=256, capacity=1920, topk=8, hidden=1024,
+                                   intermediate=512, num_tokens=4, block_m=16, ring_tokens=1920 * 40,
+                                   sf_ring_tokens=1920 * 40 * 16)
+    assert lib.gcmoe_launch_static_scratch(ctypes.byref(many_experts), ctypes.byref(bufs), None) == _native.ERR_UNSUPPORTED
+    assert 'local experts exceed the 128' in _native.last_error()
+    # 32 local experts are fine, but the tile counters of a 4096-token, top-8 ring are not
+    big_ring = _native.Problem(num_ranks=1, rank=0, num_experts=32, capacity=5760, topk=8, hidden=7168,
+                               intermediate=2048, num_tokens=4096, block_m=240, ring_tokens=376320,
+                               sf_ring_tokens=376320 * 16)
+    assert lib.gcmoe_scratch_bytes(ctypes.byref(big_ring)) > 65536
+    assert lib.gcmoe_launch_static_scratch(ctypes.byref(big_ring), ctypes.byref(bufs), None) == _native.ERR_UNSUPPORTED
+    message = _native.last_error()
+    assert 'tile counters' in message and 'ring of 376320 rows' in message and 'local experts exceed' not in message
+    assert lib.gcmoe_static_scratch_status(None, None) == _native.ERR_INVALID

@@ -192,6 +192,47 @@ def test_contract_violations_raise_like_the_reference(small):
         G.fp8_fp4_gc_moe(torch.empty((4000, small.h), dtype=torch.bfloat16, device='cuda'), small.l1, small.l2, small.buf)
 
 
+@pytest.mark.parametrize('tokens,hot', [(40, False), (300, False), (900, True)])
+def test_raw_accumulators_of_both_tile_regimes(small, tokens, hot):
+    """The FP32 accumulators of the gate/up GEMM, read straight from TMEM, against
+    an FP32 matmul of the dequantised operands: a sharper check of the MMA,
+    descriptor and scale plumbing than y.  40 tokens run one CTA per tile
+    (cta_group::1), 300 and 900 tokens CTA pairs (cta_group::2) -- with all routes
+    on two experts an expert spans several 240-token tiles."""
+    import ctypes
+    from gc_moe_b200 import _native, operator
+    from gc_moe_b200.contract import validate_call
+    xq, xsf, idx, w = O.make_tokens(tokens, small.h, small.e, small.k, seed=300 + tokens)
+    if hot:
+        idx[:, 0], idx[:, 1] = 1, 6
+    y = torch.empty((tokens, small.h), dtype=torch.bfloat16, device='cuda')
+    small.run(xq, xsf, idx, w, y=y)
+    ref = small.oracle(xq, xsf, idx, w)
+    d = ref.dispatch[0]
+    rows = d.metadata.shape[0]
+    out = torch.full((rows, 2 * small.i), float('nan'), dtype=torch.float32, device='cuda')
+    cfg = validate_call(y, small.l1, small.l2, small.buf, None, None, None, (1, 1, 32), 'swiglu', 10.0, True,
+                        None, None)
+    assert (cfg.block_m >= 64) == (tokens >= 300)
+    plan = operator.get_plan(cfg, y, small.l1, small.l2, small.buf, None, None, None)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _native.raise_for(_native.library().gcmoe_debug_gemm_l1_raw(plan.handle, out.data_ptr(), stream))
+    torch.cuda.synchronize()
+    small.buf.raise_on_device_error()
+    got = out.cpu()
+    for l in range(small.e):
+        n = int(d.counts[:, l].sum())
+        if n == 0:
+            continue
+        r0 = int(d.expert_block_start[l]) * d.block_m
+        xd = O.dequant_fp8(torch.from_numpy(d.rows[r0:r0 + n]).view(torch.float8_e4m3fn),
+                           torch.from_numpy(d.sf_words[r0:r0 + n]).view(torch.uint8))
+        wd = O.interleave_gate_up(O.dequant_fp4(small.q1[l], small.c1[l]))
+        want = xd @ wd.T
+        err = (got[r0:r0 + n] - want).abs().max().item()
+        assert err <= 1e-4 * want.abs().max().item(), (l, n, err)
+
+
 @pytest.fixture(scope='module')
 def large(single_rank_group):
     """Geometry for the large-token regime: capacity 5760 tokens, 16 experts."""

@@ -81,6 +81,36 @@ def test_static_scratch_entry_matches_plan_entry(single_rank_group):
         case.close()
 
 
+def test_static_scratch_keeps_an_earlier_failure_visible(single_rank_group):
+    """A wait that gave up leaves the workspace failed: its kernels return at once.
+    A later static-scratch call clears the status words, runs nothing and leaves y
+    alone -- the status query must still say so, not report success."""
+    import gc_moe_b200 as G
+    from gc_moe_b200 import operator
+    lib = _native.library()
+    case = LayerCase(single_rank_group, num_experts=8, hidden=1024, inter=512, topk=2, seed=22)
+    try:
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        words = (ctypes.c_uint32 * _native.STATUS_WORDS)()
+        inputs = O.make_tokens(5, case.h, case.e, case.k, seed=33)
+        case.run(*inputs)                                        # a plan to hang the expiring wait on
+        y = torch.full((5, case.h), float('nan'), dtype=torch.bfloat16, device='cuda')
+        cfg = validate_call(y, case.l1, case.l2, case.buf, None, None, None, (1, 1, 32), 'swiglu', 10.0, True,
+                            None, None)
+        plan = operator.get_plan(cfg, y, case.l1, case.l2, case.buf, None, None, None)
+        _native.raise_for(lib.gcmoe_debug_expire_wait(plan.handle, 200, stream))
+        torch.cuda.synchronize()
+        case.stage(*inputs)
+        prob, buf = describe_call(case, y, 10.0, True)
+        _native.raise_for(lib.gcmoe_launch_static_scratch(ctypes.byref(prob), ctypes.byref(buf), stream))
+        rc = lib.gcmoe_static_scratch_status(stream, words)
+        assert rc == _native.ERR_DEVICE, _native.last_error()
+        assert torch.isnan(y.float()).all()
+        case.buf._plans.clear()        # the failed plan's status would raise at close otherwise
+    finally:
+        case.close()
+
+
 def test_static_scratch_rejects_more_experts_than_it_holds():
     lib = _native.library()
     prob = _native.Problem(num_ranks=1, rank=0, num_experts=256, capacity=1920, topk=8, hidden=1024,
