@@ -312,17 +312,25 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
                                const char* what) -> int {
         const uint32_t top = pair ? max_rows / 2 : max_rows;
         const uint32_t heights[kMaxActMaps] = {8, 16, 32, 48, 64, 96, 112, 120};
-        const uint64_t adims[2] = {k, rows};
-        const uint64_t astr[1] = {k};
         sg.num_act_maps = 0;
         for (int i = 0; i < kMaxActMaps; ++i) {
             uint32_t h = heights[i];
             if (!pair && h < 16) continue;
             if (h >= top || i == kMaxActMaps - 1) h = top;
-            const uint32_t abox[2] = {128, h};
-            if (int rc = encode_map(&sg.tm_act[sg.num_act_maps], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr,
-                                    abox, what))
-                return rc;
+            int rc;
+            if (pair) {
+                // [K/128][rows][128 B] view of the row-major tensor: one request stages two K blocks
+                const uint64_t adims[3] = {128, rows, k / 128};
+                const uint64_t astr[2] = {k, 128};
+                const uint32_t abox[3] = {128, h, kPairStageBlocks};
+                rc = encode_map(&sg.tm_act[sg.num_act_maps], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, acts, adims, astr, abox, what);
+            } else {
+                const uint64_t adims[2] = {k, rows};
+                const uint64_t astr[1] = {k};
+                const uint32_t abox[2] = {128, h};
+                rc = encode_map(&sg.tm_act[sg.num_act_maps], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, acts, adims, astr, abox, what);
+            }
+            if (rc) return rc;
             sg.act_box_rows[sg.num_act_maps++] = h;
             if (h == top) break;
         }
@@ -333,7 +341,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
                           uint32_t k_blocks, uint64_t w_sf, uint64_t w_sf_stride, uint64_t w_sf_planes,
                           const char* what) -> int {
         if (!pair) return GCMOE_OK;
-        const uint32_t box[2] = {128, 1};
+        const uint32_t box[2] = {128, kPairStageBlocks};
         const uint64_t adims[2] = {act_sf_rows, k_blocks}, astr[1] = {act_sf_stride * 4};
         if (int rc = encode_map(&sg.tm_act_sf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, acts_sf, adims, astr, box, what, false))
             return rc;
@@ -370,7 +378,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         // box is one contiguous 16 KiB range in HBM.
         const uint64_t wdims[4] = {128, w_rows, k / 128, EL};
         const uint64_t wstr[3] = {64, uint64_t(w_rows) * 64, uint64_t(w_rows) * 64 * (k / 128)};
-        const uint32_t wbox[4] = {128, uint32_t(pair ? kHalfRows : kTileRows), 1, 1};
+        const uint32_t wbox[4] = {128, uint32_t(pair ? kHalfRows : kTileRows), pair ? kPairStageBlocks : 1u, 1};
         return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, weights, wdims, wstr, wbox, what);
     };
     // Shared expert: FP8 weights [K/128][rows][128 B], this rank's own tokens as rows.
@@ -401,7 +409,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
             return rc;
         const uint64_t wdims[3] = {128, w_rows, k / 128};
         const uint64_t wstr[2] = {128, uint64_t(w_rows) * 128};
-        const uint32_t wbox[3] = {128, uint32_t(pair ? kHalfRows : kTileRows), 1};
+        const uint32_t wbox[3] = {128, uint32_t(pair ? kHalfRows : kTileRows), pair ? kPairStageBlocks : 1u};
         return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, weights, wdims, wstr, wbox, what);
     };
 

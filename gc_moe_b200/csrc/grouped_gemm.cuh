@@ -15,7 +15,11 @@
 //    one thread of the leader issues tcgen05.mma.cta_group::2 for both, and each
 //    CTA's TMEM holds the accumulator of its 128 weight rows x all tokens, which
 //    its own epilogue warps drain.  Both CTAs' barriers are signalled by two plain
-//    tcgen05.commit (local, then the peer's shared::cluster address).
+//    tcgen05.commit (local, then the peer's shared::cluster address).  A pipeline
+//    stage of a pair holds two K128 blocks: the TMA unit of an SM spends about
+//    65 ns per request whatever its size (measured: four requests per stage bound
+//    the stage at 0.3 us in both regimes, independent of the MMA work), and a
+//    CTA of a pair fetches only half a weight tile per request.
 //
 // Roles (288 threads per CTA):
 //   warp 0    weight producer: per K128 stage one TMA tile (packed FP4, unpacked to
@@ -89,10 +93,11 @@ constexpr int kMaxSegments = 4;   // shared up, routed up, shared down, routed d
 // grid is resident (grid <= SMs, one CTA per SM), so the wait cannot deadlock.
 struct GemmSegment {
     CUtensorMap tm_act[kMaxActMaps];   // u8 [rows][K], box 128 x act_box_rows[i], 128-byte swizzle
+                                       // (pair: viewed as [K/128][rows][128], box 128 x rows x 2 K blocks)
     CUtensorMap tm_w;       // FP4: 16U4_ALIGN16B [E][K/128][rows][128]; FP8: u8 [K/128][rows][128];
-                            // box 128 x 256 (pair: 128 x 128, one half per CTA)
-    CUtensorMap tm_act_sf;  // pair only: u32 [K/128][act_sf_stride], box 128 x 1
-    CUtensorMap tm_w_sf;    // pair only: u32 [experts x planes][w_sf_stride], box 128 x 1
+                            // box 128 x 256 (pair: 128 x 128 x 2 K blocks, one half per CTA)
+    CUtensorMap tm_act_sf;  // pair only: u32 [K/128][act_sf_stride], box 128 x 2 K blocks
+    CUtensorMap tm_w_sf;    // pair only: u32 [experts x planes][w_sf_stride], box 128 x 2 planes
     uint32_t act_box_rows[kMaxActMaps];   // ascending; a tile fetches the smallest box that holds its rows
     uint32_t num_act_maps;
     const uint32_t* act_sf;  // packed scale words, MN-major: word (kb, r) at kb * act_sf_stride + r
@@ -165,6 +170,7 @@ struct GemmSmemLayout {
     uint32_t w, a, sfw, sfa, bars, tables, amax, arrive, feed, rows, out, total;
     uint32_t w_stage, a_stage, sfw_stage, sfa_stage;   // bytes per pipeline stage
 };
+constexpr uint32_t kPairStageBlocks = 2;   // K128 blocks per pipeline stage of a CTA pair
 
 // `block_m`: largest tile of the launch.  A CTA of a pair holds half of the
 // weight tile and half of the token tile, and the scale words of all tokens.
@@ -172,10 +178,11 @@ __host__ __device__ inline GemmSmemLayout gemm_smem_layout(uint32_t stages, uint
                                                            uint32_t sf_block_m,
                                                            uint32_t table_words, bool pair) {
     GemmSmemLayout l;
-    l.w_stage = pair ? kHalfStageBytes : 2 * kHalfStageBytes;
-    l.a_stage = round_up_u32((pair ? block_m / 2 : block_m) * kTileK, 1024);
-    l.sfw_stage = pair ? kSfChunkBytes : 2 * kSfChunkBytes;
-    l.sfa_stage = sf_block_m * 4;
+    // single CTA: both 128-row halves of one K128 block; CTA of a pair: its half, two K128 blocks
+    l.w_stage = 2 * kHalfStageBytes;
+    l.a_stage = pair ? 2 * round_up_u32(block_m / 2 * kTileK, 1024) : round_up_u32(block_m * kTileK, 1024);
+    l.sfw_stage = 2 * kSfChunkBytes;
+    l.sfa_stage = (pair ? 2 : 1) * sf_block_m * 4;
     l.w = 0;
     l.a = l.w + stages * l.w_stage;
     l.sfw = l.a + stages * l.a_stage;
@@ -541,7 +548,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 if (!__shfl_sync(0xffffffffu, done, 0)) { ok = false; break; }
                 ptx::fence_proxy_async_global();
             }
-            for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+            for (uint32_t kb = 0; kb < k_blocks; kb += kPair ? kPairStageBlocks : 1u) {
                 const bool got = mbar_wait(bar_empty + 8 * cur.stage, cur.phase ^ 1u, ctl, 1);
                 if (!got) { ok = false; break; }
                 const uint32_t full = lead_full + 8 * cur.stage;
@@ -551,17 +558,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                     if (weights) {
                         // K128-granular scales: one packed word serves four K128 blocks
                         const bool load_sf = (kb & kmask) == 0;
-                        const uint32_t tx = w_tx + (load_sf ? L.sfw_stage : 0);
                         const uint32_t dst = base + L.w + cur.stage * L.w_stage;
                         const uint32_t sf_dst = base + L.sfw + cur.stage * L.sfw_stage;
                         if constexpr (kPair) {
-                            ptx::mbar_arrive_expect_tx_cluster(full, tx);
+                            // two K128 blocks of this CTA's 128 rows per request (a block beyond K reads zeros)
+                            ptx::mbar_arrive_expect_tx_cluster(full, 2 * w_tx + (load_sf ? L.sfw_stage : 0));
                             if (fp4) ptx::tma_pair_load_4d(dst, &sg.tm_w, full, 0, w_row0, kb, e, w_hint);
                             else ptx::tma_pair_load_3d(dst, &sg.tm_w, full, 0, w_row0, kb, w_hint);
                             if (load_sf)
                                 ptx::tma_pair_load_2d(sf_dst, &sg.tm_w_sf, full, w_row0, e * sf_planes + (kb >> kshift), w_hint);
                         } else {
-                            ptx::mbar_arrive_expect_tx(full, tx);
+                            ptx::mbar_arrive_expect_tx(full, w_tx + (load_sf ? L.sfw_stage : 0));
                             if (fp4) ptx::tma_load_4d(dst, &sg.tm_w, full, 0, w_row0, kb, e, w_hint);
                             else ptx::tma_load_3d(dst, &sg.tm_w, full, 0, w_row0, kb, w_hint);
                             if (load_sf)
@@ -569,18 +576,18 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                                                   L.sfw_stage, full, w_hint);
                         }
                     } else {
-                        const uint32_t tx = act_rows * kTileK + sf_chunk * 4;
                         const uint32_t dst = base + L.a + cur.stage * L.a_stage;
                         const uint32_t sf_dst = base + L.sfa + cur.stage * L.sfa_stage;
                         if constexpr (kPair) {
-                            ptx::mbar_arrive_expect_tx_cluster(full, tx);
-                            ptx::tma_pair_load_2d(dst, act_map, full, kb * kTileK, act_row0, ptx::kEvictLast);
+                            // token rows [2 K blocks][rows][128 B]; scale words [128-row chunk][2 K blocks][128]
+                            ptx::mbar_arrive_expect_tx_cluster(full, 2 * (act_rows * kTileK + sf_chunk * 4));
+                            ptx::tma_pair_load_3d(dst, act_map, full, 0, act_row0, kb, ptx::kEvictLast);
                             ptx::tma_pair_load_2d(sf_dst, &sg.tm_act_sf, full, tc.sf_row, kb, ptx::kEvictLast);
                             if (sf_chunk > 128)
-                                ptx::tma_pair_load_2d(sf_dst + kSfChunkBytes, &sg.tm_act_sf, full, tc.sf_row + 128, kb,
+                                ptx::tma_pair_load_2d(sf_dst + 2 * kSfChunkBytes, &sg.tm_act_sf, full, tc.sf_row + 128, kb,
                                                       ptx::kEvictLast);
                         } else {
-                            ptx::mbar_arrive_expect_tx(full, tx);
+                            ptx::mbar_arrive_expect_tx(full, act_rows * kTileK + sf_chunk * 4);
                             ptx::tma_load_2d(dst, act_map, full, kb * kTileK, act_row0, ptx::kEvictLast);
                             ptx::bulk_load_1d(sf_dst, asf + static_cast<size_t>(kb) * act_sf_stride, sf_chunk * 4, full,
                                               ptx::kEvictLast);
@@ -639,7 +646,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 if (!acc_free) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (as * halves + m) * bm;
-                for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+                // rows of token operand staged per K block (pair: this CTA's box, see the producer)
+                uint32_t a_block_bytes = 0;
+                if constexpr (kPair) {
+                    uint32_t mi = 0;
+                    while (mi + 1 < sg.num_act_maps && sg.act_box_rows[mi] < n / 2) ++mi;
+                    a_block_bytes = sg.act_box_rows[mi] * kTileK;
+                }
+                for (uint32_t kb = 0; kb < k_blocks; kb += kPair ? kPairStageBlocks : 1u) {
                     const bool got = mbar_wait(bar_full + 8 * cur.stage, cur.phase, ctl, 3);
                     if (!got) { ok = false; break; }
                     ptx::tc_fence_after();
@@ -648,21 +662,39 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         // 16-byte units (all shared-memory addresses fit the 14-bit field).
                         const uint64_t sfw_desc = sfw_desc0 + cur.stage * (L.sfw_stage >> 4);
                         const uint64_t sfa_desc = sfa_desc0 + cur.stage * (L.sfa_stage >> 4);
-                        // Weight scales of K128 granularity arrive with every fourth stage and
-                        // stay in TMEM for the three stages that follow.
-                        if ((kb & kmask) == 0) ptx::tmem_cp_sf<kPair>(sfw_tmem, sfw_desc);
-                        ptx::tmem_cp_sf<kPair>(sfa_tmem, sfa_desc);
-                        if (wide_sf) ptx::tmem_cp_sf<kPair>(sfa_tmem + 4, sfa_desc + (kSfChunkBytes >> 4));
-                        // Scale byte of MMA k: k-th byte of the stage's packed words (K32 scales);
-                        // for K128 weight scales the weight byte is kb % 4 for all four.
-                        const uint32_t first = kmask ? (idesc | ((kb & 3u) << 29)) : idesc;
-                        ptx::mma_mxf8f6f4_k128<kPair>(d_tmem, wdesc0 + cur.stage * (L.w_stage >> 4),
-                                                      adesc0 + cur.stage * (L.a_stage >> 4), first,
-                                                      kmask ? (1u << 4) : ((1u << 29) | (1u << 4)), sfw_tmem, sfa_tmem,
-                                                      kb != 0u ? 1u : 0u);
+                        const uint64_t wdesc = wdesc0 + cur.stage * (L.w_stage >> 4);
+                        const uint64_t adesc = adesc0 + cur.stage * (L.a_stage >> 4);
+                        const uint32_t step = kmask ? (1u << 4) : ((1u << 29) | (1u << 4));
+                        if constexpr (kPair) {
+#pragma unroll
+                            for (uint32_t j = 0; j < kPairStageBlocks; ++j) {
+                                const uint32_t k = kb + j;
+                                if (k < k_blocks) {
+                                    // weight scales of K128 granularity: one word per four K blocks
+                                    if ((k & kmask) == 0) ptx::tmem_cp_sf<kPair>(sfw_tmem, sfw_desc + (kmask ? 0u : j * (kSfChunkBytes >> 4)));
+                                    ptx::tmem_cp_sf<kPair>(sfa_tmem, sfa_desc + j * (kSfChunkBytes >> 4));
+                                    if (wide_sf) ptx::tmem_cp_sf<kPair>(sfa_tmem + 4, sfa_desc + (2 + j) * (kSfChunkBytes >> 4));
+                                    const uint32_t first = kmask ? (idesc | ((k & 3u) << 29)) : idesc;
+                                    ptx::mma_mxf8f6f4_k128<kPair>(d_tmem, wdesc + j * (kHalfStageBytes >> 4),
+                                                                  adesc + j * (a_block_bytes >> 4), first, step, sfw_tmem,
+                                                                  sfa_tmem, k != 0u ? 1u : 0u);
+                                }
+                            }
+                        } else {
+                            // Weight scales of K128 granularity arrive with every fourth stage and
+                            // stay in TMEM for the three stages that follow.
+                            if ((kb & kmask) == 0) ptx::tmem_cp_sf<kPair>(sfw_tmem, sfw_desc);
+                            ptx::tmem_cp_sf<kPair>(sfa_tmem, sfa_desc);
+                            if (wide_sf) ptx::tmem_cp_sf<kPair>(sfa_tmem + 4, sfa_desc + (kSfChunkBytes >> 4));
+                            // Scale byte of MMA k: k-th byte of the stage's packed words (K32 scales);
+                            // for K128 weight scales the weight byte is kb % 4 for all four.
+                            const uint32_t first = kmask ? (idesc | ((kb & 3u) << 29)) : idesc;
+                            ptx::mma_mxf8f6f4_k128<kPair>(d_tmem, wdesc, adesc, first, step, sfw_tmem, sfa_tmem,
+                                                          kb != 0u ? 1u : 0u);
+                        }
                         ptx::tc_commit<kPair>(bar_empty + 8 * cur.stage);
                         if constexpr (kPair) ptx::tc_commit<kPair>(peer_empty + 8 * cur.stage);
-                        if (kb + 1 == k_blocks) {
+                        if (kb + (kPair ? kPairStageBlocks : 1u) >= k_blocks) {
                             ptx::tc_commit<kPair>(bar_acc_full + 8 * as);
                             if constexpr (kPair) ptx::tc_commit<kPair>(peer_acc_full + 8 * as);
                         }

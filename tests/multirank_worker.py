@@ -30,6 +30,15 @@ def main():
     os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
     dist.init_process_group('nccl', device_id=dev)
     group = dist.group.WORLD
+    host_group = dist.new_group(backend='gloo')     # host-side decisions (who failed) never touch the GPUs
+
+    def anyone_failed():
+        """Every rank learns whether ANY rank has recorded a failure, so that all of them
+        skip the remaining collective calls together instead of leaving peers to wait
+        for a rank that has gone."""
+        flag = torch.tensor([1 if failures else 0])
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=host_group)
+        return bool(flag.item())
     E, H, I, K, CAP = 8 * world, 1024, 512, 4, 1920
     EL = E // world
 
@@ -57,6 +66,9 @@ def main():
         if case.get('hot') is not None and tokens:
             idx[:, 0] = case['hot']
             idx[:, 1] = (case['hot'] + 1) % E
+        if case.get('to_rank0') and tokens:
+            idx = idx % EL             # every route goes to an expert of rank 0
+            idx[:, 1:] = (idx[:, :1] + torch.arange(1, K)) % EL   # k distinct experts per token
         return xq, xsf, idx, w
 
     def stage(inp):
@@ -76,7 +88,23 @@ def main():
         {'name': 'invalid_routes', 'tokens': [20] * world, 'seed': 4, 'invalid': True},
         {'name': 'hot_expert', 'tokens': [150] * world, 'seed': 5, 'hot': 1},
         {'name': 'single_token', 'tokens': [1] * world, 'seed': 6},
+        # the reference's asymmetric vectors (scripts/run.sh:313-391): nobody, one rank only,
+        # a ramp, ranks in different tile regimes (block-M 16 next to 96)
+        {'name': 'all_idle', 'tokens': [0] * world, 'seed': 7},
+        {'name': 'one_active', 'tokens': [33 if r == world - 1 else 0 for r in range(world)], 'seed': 8},
+        {'name': 'ramp', 'tokens': [5 + 40 * r for r in range(world)], 'seed': 9},
+        {'name': 'mixed_regimes', 'tokens': [400 if r % 2 else 3 for r in range(world)], 'seed': 10},
+        # one rank enters the call late, with no barrier in front: its peers' GEMM launches
+        # (and their down tiles) run while its rows are still on their way
+        {'name': 'late_rank', 'tokens': [48] * world, 'seed': 11, 'late': world - 1, 'hot': 2},
+        {'name': 'late_rank_decode', 'tokens': [2] * world, 'seed': 12, 'late': 0},
     ]
+    # every block-M switch of this geometry, one token either side (scripts/run.sh:292-311)
+    switches = [t for t in range(1, 700)
+                if G.get_block_m_for_gc_moe(world, E, CAP, t, K) != G.get_block_m_for_gc_moe(world, E, CAP, t - 1, K)]
+    for t in switches[:6]:
+        cases.append({'name': f'boundary_{t - 1}', 'tokens': [t - 1] * world, 'seed': 100 + t})
+        cases.append({'name': f'boundary_{t}', 'tokens': [t] * world, 'seed': 200 + t})
     expected_stats = np.zeros(EL, np.int64)
     for case in cases:
         all_inputs = [inputs_of(case, r) for r in range(world)]
@@ -88,12 +116,16 @@ def main():
         y = torch.full((t, H), float('nan'), dtype=torch.bfloat16, device=dev)
         gen = int(buf.region('recv_parity').view(torch.int32)[0].item()) & 1
         dist.barrier()
+        if case.get('late') == rank:
+            import time
+            time.sleep(0.05)           # host-side skew only: the GPUs keep running
         G.fp8_fp4_gc_moe(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=10.0)
         torch.cuda.synchronize()
         try:
             buf.raise_on_device_error()
         except RuntimeError as exc:
             failures.append(f"{case['name']}: {exc}")
+        if anyone_failed():
             break
         dist.barrier()
         d, bm = ref.dispatch[rank], bms[rank]
@@ -120,12 +152,16 @@ def main():
             cos, err = O.cosine(yc, ref.y[rank]), O.max_rel_err(yc, ref.y[rank])
             report[case['name']] = [round(cos, 9), err]
             check(case['name'] + ':y', bool(torch.isfinite(yc.float()).all()) and cos >= COSINE_MIN and err <= MAX_REL_ERR)
-    check('stats', np.array_equal(stats.cpu().numpy(), expected_stats))
+    if not anyone_failed():
+        check('stats', np.array_equal(stats.cpu().numpy(), expected_stats))
 
-    # Graph capture + alternating replays at fixed addresses.
-    if not failures:
-        a = {'tokens': [12] * world, 'seed': 21}
-        b = {'tokens': [12] * world, 'seed': 22}
+    # Graph capture + alternating replays at fixed addresses, all routed work of every
+    # rank sent to rank 0's experts (the reference's readiness protocol,
+    # tests/test_gc_moe_readiness.py:97-99,148,165-178): y is pre-filled with NaN and
+    # each replay must reproduce its own eager result, not the other input's.
+    if not anyone_failed():
+        a = {'tokens': [12] * world, 'seed': 21, 'to_rank0': True}
+        b = {'tokens': [12] * world, 'seed': 22, 'to_rank0': True}
         y = torch.empty((12, H), dtype=torch.bfloat16, device=dev)
         eager = []
         for case in (a, b):
@@ -140,7 +176,8 @@ def main():
             with torch.cuda.graph(graph, stream=side):
                 G.fp8_fp4_gc_moe(y, l1, l2, buf, activation_clamp=10.0)
         torch.cuda.current_stream().wait_stream(side)
-        for it in range(10):
+        assert not torch.equal(eager[0], eager[1])
+        for it in range(40):
             stage(inputs_of((a, b)[it & 1], rank))
             y.fill_(float('nan'))
             torch.cuda.synchronize(); dist.barrier()
@@ -154,7 +191,7 @@ def main():
         dist.barrier()
     # Fused shared expert together with expert parallelism: every rank applies the
     # (replicated) shared expert to its own tokens while its routes go to their owners.
-    if not failures:
+    if not anyone_failed():
         sbuf = G.get_symm_buffer_for_gc_moe(group, E, CAP, K, H, I, 1)
         gs = torch.Generator().manual_seed(11)
         sw1, sc1 = O.quantize_block_fp8(torch.randn((2 * I, H), generator=gs) * 0.02)
