@@ -699,7 +699,7 @@ def headline(env: Env, args):
         'tokens_per_s_by_tokens': {str(t): round(env.world * t / (latency[t] * 1e-6)) for t in sweep},
         'e2e': {'value': round(e2e_us, 2) if e2e_us is not None else None, 'unit': 'us',
                 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': d2h},
-        'gpu_launches': args.steps * n * lb.lib.gcmoe_kernels_per_launch(lb.plans[sweep[0]].handle),
+        'gpu_launches': args.steps * sum(lb.lib.gcmoe_kernels_per_launch(lb.plans[t].handle) for t in sweep),
         'roofline': roofline, 'clocks': clocks.summary(), 'wall_s_timed_region': round(wall, 3),
     }
     return line, lb

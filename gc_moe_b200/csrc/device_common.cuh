@@ -129,7 +129,9 @@ enum CallInfoWord : int {
     kCallEpoch = 2,
     kCallTablesReady = 3,     // epoch + 1 once the tables of this call are in place (release by dispatch CTA 0):
                               // the GEMM launch starts while the dispatch kernel is still pushing rows
-    kCallTileCursor = 4,      // tiles claimed by the running GEMM launch beyond one per CTA (back to 0 when it ends)
+    kCallTileCursor = 4,
+    kCallPairRegime = 5,      // 1: the GEMM launch of the pair regime does this call's work, 0: the single one
+    kCallTileCursorPair = 6,  // tile cursor of the pair regime's launch (the two launches of a call can overlap)      // tiles claimed by the running GEMM launch beyond one per CTA (back to 0 when it ends)
     kCallInfoWords = 8
 };
 
@@ -156,16 +158,24 @@ __host__ __device__ __forceinline__ uint32_t bytes(uint32_t ranks, uint32_t expe
 }
 }  // namespace exchange
 
-// Two regimes of the expert GEMMs, chosen per rank from the block-M of its pool
-// (every sender knows every owner's block-M, so all ranks agree):
-//  * decode (block-M below 64): one CTA per tile, cta_group::1, tiles of up to 64
-//    tokens.  A tcgen05.mma costs the same issue time for 16 columns as for 64,
-//    and the kernel is bound by weight streaming and instruction issue.
-//  * large-token (block-M 64 and above): a CTA pair per tile, cta_group::2.  The
-//    pair's MMA covers 256 weight rows and up to 240 tokens with the token
-//    operand split over the two CTAs, so one fetch of a weight tile from shared
-//    memory serves twice the tokens a single CTA's 112-token tile could, and two
-//    accumulator stages of 240 columns fit each CTA's TMEM.
+// Two regimes of the expert GEMMs:
+//  * single: one CTA per tile, cta_group::1, tiles of up to 64 tokens.  A tcgen05.mma
+//    costs the same issue time for 16 columns as for 64, and the kernel is bound by
+//    weight streaming: the regime of decode and of evenly spread routing.
+//  * pair: a CTA pair per tile, cta_group::2.  The pair's MMA covers 256 weight rows
+//    and up to 240 tokens with the token operand split over the two CTAs, so one
+//    fetch of a weight tile serves up to 240 tokens, and two accumulator stages of
+//    240 columns fit each CTA's TMEM: the regime of experts with hundreds of rows
+//    (large token counts, skewed routing).  It streams the weights of experts with
+//    few rows at about half the rate of the single regime (a CTA of a pair fetches
+//    half a weight tile per request), so it only pays when most rows sit in large
+//    experts.
+// The regime of a rank is chosen per call ON THE DEVICE, from the rows its experts
+// actually received: small calls are always single (dual_regime_call); otherwise
+// pair when at least half of the rank's rows belong to experts with
+// kPairExpertRows rows or more.  Every rank evaluates this for every owner from the exchanged count matrix
+// (senders need the owner's tile geometry), so all ranks agree.  The host enqueues
+// the GEMM launch of both regimes; the one that was not chosen returns at once.
 // GEMM tiles are independent of the pool blocks: an expert's rows are contiguous
 // in the pool, and its tiles are sized from its own row count so that an expert
 // with many rows costs as few passes over its weights as possible.  The scale
@@ -179,24 +189,36 @@ __host__ __device__ __forceinline__ uint32_t bytes(uint32_t ranks, uint32_t expe
 #endif
 constexpr uint32_t kPairMinBlockM = GCMOE_PAIR_MIN_BLOCK_M;
 constexpr uint32_t kPairTileRows = GCMOE_PAIR_TILE_ROWS;
+constexpr uint32_t kPairExpertRows = 128;
 constexpr uint32_t kSingleTileRows = 64;
-__host__ __device__ __forceinline__ bool pair_mode(uint32_t block_m) { return block_m >= kPairMinBlockM; }
+constexpr uint32_t kDualMinRoutes = 4096;
+// Whether a call enqueues the launches of both regimes (host; the flag travels to the other ranks
+// with the block-M): calls large enough for some expert to collect hundreds of rows -- block-M 64
+// and above, or 4096 routes in the group (taking this rank's token count for every rank).  Below
+// that the second launch's few microseconds would not be earned back.
+__host__ __device__ __forceinline__ bool dual_regime_call(uint32_t block_m, uint64_t group_routes) {
+    return block_m >= kPairMinBlockM || group_routes >= kDualMinRoutes;
+}
+// the regime of one call: rows_in_large = rows of experts with >= kPairExpertRows rows
+__host__ __device__ __forceinline__ bool pair_chosen(bool dual, uint32_t rows_in_large, uint32_t rows) {
+    return dual && rows != 0u && 2u * rows_in_large >= rows;
+}
+constexpr uint32_t kBlockMDualFlag = 0x10000u;   // set in the exchanged block-M word of a rank whose call is dual
 
 __host__ __device__ __forceinline__ uint32_t round_up_u32(uint32_t v, uint32_t m) {
     return (v + m - 1) / m * m;
 }
-// Rows per GEMM tile of an expert that received `n` rows on a rank whose pool
-// uses `block_m` (tile t covers rows [t * rows, ...)).  Depends only on values
-// every rank knows.
-__host__ __device__ __forceinline__ uint32_t expert_tile_rows(uint32_t block_m, uint32_t n) {
-    if (!pair_mode(block_m)) return kSingleTileRows;
+// Rows per GEMM tile of an expert that received `n` rows, in the given regime
+// (tile t covers rows [t * rows, ...)).
+__host__ __device__ __forceinline__ uint32_t expert_tile_rows(bool pair, uint32_t n) {
+    if (!pair) return kSingleTileRows;
     if (n <= kPairTileRows) return n <= 16u ? 16u : round_up_u32(n, 16u);
     const uint32_t tiles = (n + kPairTileRows - 1u) / kPairTileRows;
     return round_up_u32((n + tiles - 1u) / tiles, 16u);
 }
 // Without room for the tile-ordered scale copy the tiles are the pool blocks.
-__host__ __device__ __forceinline__ uint32_t routed_tile_rows(uint32_t block_m, uint32_t n, bool tile_ordered) {
-    return tile_ordered ? expert_tile_rows(block_m, n) : block_m;
+__host__ __device__ __forceinline__ uint32_t routed_tile_rows(uint32_t block_m, uint32_t n, bool tile_ordered, bool pair) {
+    return tile_ordered ? expert_tile_rows(pair, n) : block_m;
 }
 
 // Row, inside a 128-row-aligned scale block, of the block's u-th token: the

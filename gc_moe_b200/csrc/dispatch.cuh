@@ -66,16 +66,17 @@ struct DispatchParams {
     uint32_t num_ranks, rank, num_experts, local_experts;
     uint32_t num_tokens, topk, hidden, capacity;
     uint32_t block_m, sf_ring;    // sf_ring: words between K128 planes of l1_acts_sf
+    uint32_t dual;                // the launches of both GEMM regimes are enqueued for this call
     uint32_t private_sf_row;      // row offset, in each scale plane, of the tile-ordered scale copy (0 = none)
 };
 
 // Dynamic shared memory: seven u32 per expert (own count, own routes before the
 // slice, total over sources, routes of lower sources, first pool block, first
-// GEMM tile, first tile-ordered scale row), one block-M per rank, then the CTA's
-// slice: expert id, pool row and position inside the expert per route.
+// GEMM tile, first tile-ordered scale row), one block-M and one GEMM regime per rank,
+// then the CTA's slice: expert id, pool row and position inside the expert per route.
 __host__ __device__ inline uint32_t dispatch_smem_bytes(uint32_t num_experts, uint32_t num_ranks,
                                                         uint32_t slice) {
-    return (7 * num_experts + num_ranks + 8 + 3 * slice) * 4;
+    return (7 * num_experts + 2 * num_ranks + 8 + 3 * slice) * 4;
 }
 
 __global__ void __launch_bounds__(kDispatchThreads)
@@ -93,7 +94,8 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     uint32_t* const first_tile = first_block + E;   // [E] first GEMM tile of the expert at its owner
     uint32_t* const first_sf = first_tile + E;  // [E] first row of the expert's tile-ordered scale chunks at its owner
     uint32_t* const bm_of = first_sf + E;       // [P] block-M of each rank's pool
-    uint32_t* const misc = bm_of + P;           // [8] abort word, own pool blocks, own valid routes
+    uint32_t* const pair_of = bm_of + P;        // [P] 1: the rank's GEMMs run in the pair regime for this call
+    uint32_t* const misc = pair_of + P;         // [8] abort word, own pool blocks, own valid routes
     int* const slice_expert = reinterpret_cast<int*>(misc + 8);
     uint32_t* const slice_row = reinterpret_cast<uint32_t*>(slice_expert + slice);
     uint32_t* const slice_pos = slice_row + slice;
@@ -139,7 +141,8 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
                                      (static_cast<size_t>(gen) * P + p.rank) * E;
             for (uint32_t e = tid; e < E; e += kDispatchThreads) counts[e] = own[e];
             if (tid == 0)
-                reinterpret_cast<uint32_t*>(ex + exchange::kSourceBlockM)[gen * kMaxRanks + p.rank] = p.block_m;
+                reinterpret_cast<uint32_t*>(ex + exchange::kSourceBlockM)[gen * kMaxRanks + p.rank] =
+                    p.block_m | (p.dual ? kBlockMDualFlag : 0u);
         }
         __syncthreads();
         // One thread per served peer raises that peer's flag, all at once: each release
@@ -178,7 +181,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             bm_of[s] = reinterpret_cast<const uint32_t*>(ex + exchange::kSourceBlockM)[gen * kMaxRanks + s];
     } else {
         for (uint32_t e = tid; e < E; e += kDispatchThreads) { total[e] = own[e]; lower[e] = 0; }
-        if (tid == 0) bm_of[0] = p.block_m;
+        if (tid == 0) bm_of[0] = p.block_m | (p.dual ? kBlockMDualFlag : 0u);
     }
     __syncthreads();
 
@@ -189,13 +192,28 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     // (the tile's rows rounded up to 128) in the tile-ordered copy.
     const bool tile_ordered = p.private_sf_row != 0u;
     for (uint32_t r = warp; r < P; r += kDispatchThreads / 32) {
-        const uint32_t bm = bm_of[r], base = r * EL;
+        const uint32_t word = bm_of[r], bm = word & 0xFFFFu, base = r * EL;
+        __syncwarp();
+        if (lane == 0) bm_of[r] = bm;          // from here on the plain block-M
         const uint32_t per_lane = (EL + 31) / 32;
+        // the owner's GEMM regime for this call, from the rows its experts received
+        uint32_t rows_all = 0, rows_large = 0;
+        for (uint32_t l = lane; l < EL; l += 32) {
+            const uint32_t n = total[base + l];
+            rows_all += n;
+            rows_large += n >= kPairExpertRows ? n : 0u;
+        }
+        for (uint32_t d = 16; d > 0; d >>= 1) {
+            rows_all += __shfl_xor_sync(0xffffffffu, rows_all, d);
+            rows_large += __shfl_xor_sync(0xffffffffu, rows_large, d);
+        }
+        const bool pair = pair_chosen((word & kBlockMDualFlag) != 0u, rows_large, rows_all);
+        if (lane == 0) pair_of[r] = pair ? 1u : 0u;
         uint32_t sum = 0, tsum = 0, ssum = 0;
         for (uint32_t i = 0; i < per_lane; ++i) {
             const uint32_t l = lane * per_lane + i;
             if (l < EL) {
-                const uint32_t n = total[base + l], tn = routed_tile_rows(bm, n, tile_ordered);
+                const uint32_t n = total[base + l], tn = routed_tile_rows(bm, n, tile_ordered, pair);
                 sum += (n + bm - 1) / bm;
                 tsum += (n + tn - 1) / tn;
                 ssum += (n + tn - 1) / tn * round_up_u32(tn, 128);
@@ -212,7 +230,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         for (uint32_t i = 0; i < per_lane; ++i) {
             const uint32_t l = lane * per_lane + i;
             if (l < EL) {
-                const uint32_t n = total[base + l], tn = routed_tile_rows(bm, n, tile_ordered);
+                const uint32_t n = total[base + l], tn = routed_tile_rows(bm, n, tile_ordered, pair);
                 first_block[base + l] = run;
                 first_tile[base + l] = trun;
                 first_sf[base + l] = srun;
@@ -277,6 +295,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             p.call_info[kCallGeneration] = gen;
             p.call_info[kCallCombineRows] = misc[2];
             p.call_info[kCallEpoch] = epoch;
+            p.call_info[kCallPairRegime] = pair_of[p.rank];
             if (p.shared_table != nullptr) {
                 p.shared_table[0] = static_cast<int>(p.num_tokens);
                 p.shared_table[1] = 0;
@@ -369,7 +388,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         const uint32_t sf_row = block * sf_block + sf_row_in_block(u);
         uint32_t* sf_dst = reinterpret_cast<uint32_t*>(dst_arena + p.off_l1_acts_sf);
         // second copy, ordered by GEMM tile: the one the owner's GEMM launch reads
-        const uint32_t tn = routed_tile_rows(bm, total[e], tile_ordered);
+        const uint32_t tn = routed_tile_rows(bm, total[e], tile_ordered, pair_of[owner] != 0u);
         const uint32_t pos = slice_pos[a - lo];
         const uint32_t tile_row = p.private_sf_row + first_sf[e] + (pos / tn) * round_up_u32(tn, 128) +
                                   sf_row_in_block(pos % tn);

@@ -84,11 +84,14 @@ struct Plan {
     int num_sms = 0;
     uint32_t* status = nullptr;
     DispatchParams dispatch;
-    GemmParams up, down, fused;   // up tiles only, down tiles only, the layer's single GEMM launch
+    // Launch set of one GEMM regime: up tiles only, down tiles only, the layer's single GEMM launch.
+    struct Regime {
+        GemmParams up, down, fused;
+        uint32_t grid = 0, smem = 0;      // grid 0: this regime is never launched for this plan
+    };
+    Regime single, pairs;         // one CTA per tile (cta_group::1); CTA pairs (clusters of two, cta_group::2)
     CombineParams combine;
     uint32_t dispatch_grid = 1, dispatch_smem = 0;
-    uint32_t gemm_grid = 1, gemm_smem = 0;
-    bool pair = false;            // the GEMM launch runs as CTA pairs (clusters of two, cta_group::2)
     uint32_t combine_grid = 1;
 };
 
@@ -221,11 +224,6 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     const uint32_t private_sf_row =
         (uint64_t(q.ring_tokens) / 120 + EL + 1) * 256 <= uint64_t(half_sf) ? half_sf : 0u;
     const bool tile_ordered = private_sf_row != 0u;
-    const bool pair = pair_mode(bm);
-    plan->pair = pair;
-    // largest tile of the launch: accumulator stride, rows of an activation stage
-    const uint32_t tn = tile_ordered ? (pair ? kPairTileRows : (bm > kSingleTileRows ? bm : kSingleTileRows)) : bm;
-    const uint32_t sftn = round_up_u32(tn, 128);
 
     // ---- dispatch
     DispatchParams& d = plan->dispatch;
@@ -267,16 +265,32 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     if (plan->dispatch_smem > uint32_t(kSmemLimit))
         return bail(fail(GCMOE_ERR_UNSUPPORTED, "dispatch slice does not fit shared memory"));
 
-    // ---- the two grouped GEMMs (each: shared-expert segment first, then routed)
+    // ---- the two grouped GEMMs (each: shared-expert segment first, then routed), once per regime
     const uint32_t S = q.num_shared_experts, IS = S * I;
+    int* shared_table = reinterpret_cast<int*>(call_info + kCallInfoWords);   // count, start[0], start[1], row start, scale start
+    // Per-row-tile counters of finished up tiles (zeroed by the dispatch kernel).
+    uint32_t* done_routed = reinterpret_cast<uint32_t*>(shared_table + 8);
+    uint32_t* done_shared = done_routed + q.ring_tokens / 16 + EL + 1;
+    d.done_routed = done_routed;
+    d.done_shared = S ? done_shared : nullptr;
+    d.shared_table = S ? shared_table : nullptr;
+    // Small calls only ever run the single regime; for the others the dispatch kernel chooses
+    // per call and both launches are enqueued.
+    const bool dual = dual_regime_call(bm, uint64_t(P) * q.num_tokens * q.topk);
+    d.dual = dual ? 1u : 0u;
+    auto build_regime = [&](const bool pair, Plan::Regime& out) -> int {
+    // largest tile of the launch: accumulator stride, rows of an activation stage
+    const uint32_t widest = pair ? kPairTileRows : kSingleTileRows;
+    const uint32_t tn = tile_ordered ? (S && bm > widest ? bm : widest) : bm;
+    const uint32_t sftn = round_up_u32(tn, 128);
     const uint32_t table_words = 2 * ((4 * EL + 1) + (S ? 5 : 0));   // up and down segments each hold a copy
     const uint32_t stages = gemm_pick_stages(tn, sftn, table_words, pair);
-    if (stages < 2) return bail(fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm));
-    plan->gemm_smem = gemm_smem_layout(stages, tn, sftn, table_words, pair).total + 1024;
+    if (stages < 2) return fail(GCMOE_ERR_UNSUPPORTED, "block_m %u leaves no room for two pipeline stages", bm);
+    out.smem = gemm_smem_layout(stages, tn, sftn, table_words, pair).total + 1024;
     // Two accumulator stages (epilogue overlaps the next tile) while they fit TMEM.
     const uint32_t acc_stages = gemm_tmem_columns(tn, sftn, 2, pair) <= 512 ? 2u : 1u;
     if (gemm_tmem_columns(tn, sftn, acc_stages, pair) > 512)
-        return bail(fail(GCMOE_ERR_UNSUPPORTED, "TMEM budget exceeded"));
+        return fail(GCMOE_ERR_UNSUPPORTED, "TMEM budget exceeded");
 
     auto fill_common = [&](GemmParams& g) {
         memset(&g, 0, sizeof(g));
@@ -297,8 +311,9 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.rank = q.rank;
         g.num_ranks = P;
         g.call_info = call_info;
+        g.dual_regime = dual ? 1u : 0u;
         g.epoch_word = reinterpret_cast<const uint32_t*>(arena + b.off_recv_parity);
-        g.tile_cursor = call_info + kCallTileCursor;
+        g.tile_cursor = call_info + (pair ? kCallTileCursorPair : kCallTileCursor);
         g.rows_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kRowsArrived);
         g.failed = reinterpret_cast<uint32_t*>(arena + b.off_exchange + exchange::kFailed);
         for (uint32_t r = 0; r < P; ++r) {
@@ -382,7 +397,6 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 4, weights, wdims, wstr, wbox, what);
     };
     // Shared expert: FP8 weights [K/128][rows][128 B], this rank's own tokens as rows.
-    int* shared_table = reinterpret_cast<int*>(call_info + kCallInfoWords);   // count, start[0], start[1], row start, scale start
     auto shared_segment = [&](GemmSegment& sg, uint64_t acts, uint64_t acts_sf, uint32_t k, uint64_t weights,
                               uint64_t w_sf, uint64_t w_sf_stride, uint32_t w_rows, const char* what) -> int {
         sg.shared = 1;
@@ -413,11 +427,6 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         return encode_map(&sg.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, weights, wdims, wstr, wbox, what);
     };
 
-    // Per-row-tile counters of finished up tiles (zeroed by the dispatch kernel).
-    uint32_t* done_routed = reinterpret_cast<uint32_t*>(shared_table + 8);
-    uint32_t* done_shared = done_routed + q.ring_tokens / 16 + EL + 1;
-    d.done_routed = done_routed;
-    d.done_shared = S ? done_shared : nullptr;
     // a CTA of a pair finishes one half of an up tile
     const uint32_t done_per_tile = pair ? 2u : 1u;
 
@@ -428,7 +437,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     memset(&routed_down, 0, sizeof(GemmSegment));
     if (S) {
         if (int rc = shared_segment(shared_up, arena + b.off_x, arena + b.off_shared_l1_acts_sf, H, b.sw1, b.sw1_sf,
-                                    b.sw1_sf_stride, 2 * IS, "shared gate/up GEMM")) return bail(rc);
+                                    b.sw1_sf_stride, 2 * IS, "shared gate/up GEMM")) return rc;
         shared_up.kind = kSegUp;
         shared_up.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_shared_l2_acts);
         shared_up.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_shared_l2_acts_sf);
@@ -436,13 +445,13 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         shared_up.inter = IS;
         shared_up.block_done = done_shared;
         if (int rc = shared_segment(shared_down, arena + b.off_shared_l2_acts, arena + b.off_shared_l2_acts_sf, IS,
-                                    b.sw2, b.sw2_sf, b.sw2_sf_stride, H, "shared down GEMM")) return bail(rc);
+                                    b.sw2, b.sw2_sf, b.sw2_sf_stride, H, "shared down GEMM")) return rc;
         shared_down.kind = kSegDown;
         shared_down.block_done = done_shared;
         shared_down.done_target = shared_up.n_tiles * done_per_tile;
     }
     if (int rc = routed_segment(routed_up, arena + b.off_l1_acts, arena + b.off_l1_acts_sf, H, b.w1, b.w1_sf,
-                                b.w1_sf_stride, 2 * I, "gate/up GEMM")) return bail(rc);
+                                b.w1_sf_stride, 2 * I, "gate/up GEMM")) return rc;
     routed_up.kind = kSegUp;
     routed_up.out_acts = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts);
     routed_up.out_sf = reinterpret_cast<uint8_t*>(arena + b.off_l2_acts_sf);
@@ -451,24 +460,23 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     routed_up.route_weight = reinterpret_cast<const float*>(arena + b.off_l1_topk_weights);
     routed_up.block_done = done_routed;
     if (int rc = routed_segment(routed_down, arena + b.off_l2_acts, arena + b.off_l2_acts_sf, I, b.w2, b.w2_sf,
-                                b.w2_sf_stride, H, "down GEMM")) return bail(rc);
+                                b.w2_sf_stride, H, "down GEMM")) return rc;
     routed_down.kind = kSegDown;
     routed_down.metadata = reinterpret_cast<const uint32_t*>(arena + b.off_metadata);
     routed_down.block_done = done_routed;
     routed_down.done_target = routed_up.n_tiles * done_per_tile;
 
-    fill_common(plan->up);
-    fill_common(plan->down);
-    fill_common(plan->fused);
+    fill_common(out.up);
+    fill_common(out.down);
+    fill_common(out.fused);
     auto push = [](GemmParams& g, const GemmSegment& sg) { g.seg[g.num_segments++] = sg; };
-    if (S) { push(plan->up, shared_up); push(plan->fused, shared_up); }
-    push(plan->up, routed_up);
-    push(plan->fused, routed_up);
-    if (S) { push(plan->fused, shared_down); shared_down.done_target = 0; push(plan->down, shared_down); }
-    push(plan->fused, routed_down);
+    if (S) { push(out.up, shared_up); push(out.fused, shared_up); }
+    push(out.up, routed_up);
+    push(out.fused, routed_up);
+    if (S) { push(out.fused, shared_down); shared_down.done_target = 0; push(out.down, shared_down); }
+    push(out.fused, routed_down);
     routed_down.done_target = 0;          // launched on its own, the up tiles finished in an earlier kernel
-    push(plan->down, routed_down);
-    d.shared_table = S ? shared_table : nullptr;
+    push(out.down, routed_down);
 
     // Upper bound of pool blocks this call can produce: one partial block per
     // expert that can be hit, plus the full blocks.
@@ -488,7 +496,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(plan->num_sms & ~1);
             cfg.blockDim = dim3(kGemmThreads);
-            cfg.dynamicSmemBytes = plan->gemm_smem;
+            cfg.dynamicSmemBytes = out.smem;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
@@ -497,14 +505,19 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
             int clusters = 0;
             cudaError_t oe = cudaOccupancyMaxActiveClusters(&clusters, grouped_gemm_kernel<false, true>, &cfg);
             if (oe != cudaSuccess || clusters < 1)
-                return bail(fail(GCMOE_ERR_CUDA, "cudaOccupancyMaxActiveClusters: %s (%d clusters)",
-                                 cudaGetErrorString(oe), clusters));
+                return fail(GCMOE_ERR_CUDA, "cudaOccupancyMaxActiveClusters: %s (%d clusters)",
+                            cudaGetErrorString(oe), clusters);
             grid &= ~1u;
             if (grid < 2) grid = 2;
             if (grid > uint32_t(clusters) * 2) grid = uint32_t(clusters) * 2;
         }
-        plan->gemm_grid = grid;
+        out.grid = grid;
     }
+    return GCMOE_OK;
+    };   // build_regime
+    if (int rc = build_regime(false, plan->single)) return bail(rc);
+    if (dual)
+        if (int rc = build_regime(true, plan->pairs)) return bail(rc);
 
     // ---- combine
     CombineParams& c = plan->combine;
@@ -534,10 +547,6 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
 extern "C" int gcmoe_plan_destroy(gcmoe_plan* plan) {
     delete plan;
     return GCMOE_OK;
-}
-
-extern "C" int gcmoe_kernels_per_launch(const gcmoe_plan* plan) {
-    return plan == nullptr ? 0 : 3;
 }
 
 // Launch with programmatic stream serialization: the kernel may start while
@@ -573,13 +582,38 @@ static cudaError_t launch_dependent(void (*kernel)(Params), uint32_t grid, uint3
     return cudaLaunchKernelEx(&cfg, kernel, params);
 }
 
-template <bool kRaw>
-static cudaError_t launch_gemm(const gcmoe::Plan* plan, const GemmParams& g, cudaStream_t s, bool dependent) {
-    if (plan->pair)
-        return launch_dependent(grouped_gemm_kernel<kRaw, true>, plan->gemm_grid, kGemmThreads, plan->gemm_smem, s, g,
-                                dependent, 2);
-    return launch_dependent(grouped_gemm_kernel<kRaw, false>, plan->gemm_grid, kGemmThreads, plan->gemm_smem, s, g,
+// The GEMM launch(es) of a plan: the pair regime first when the plan has one, then the
+// single regime; the dispatch kernel's choice decides which of the two does the work.
+// `pick` selects the parameter set of a regime (up, down or fused tiles).
+template <bool kRaw, typename Pick>
+static cudaError_t launch_gemms(const gcmoe::Plan* plan, Pick pick, cudaStream_t s, bool dependent, bool wait_tables,
+                                float* raw_out) {
+    auto prepare = [&](const gcmoe::Plan::Regime& regime) {
+        GemmParams g = pick(regime);
+        // Launched together with the call's dispatch kernel the GEMMs start while it runs and
+        // wait for its tables; launched alone they find the tables of the last call in place.
+        g.wait_tables = wait_tables ? 1u : 0u;
+        if (kRaw) {
+            g.seg[0] = g.seg[g.num_segments - 1];   // the routed gate/up segment alone
+            g.num_segments = 1;
+            g.raw_out = raw_out;
+        }
+        return g;
+    };
+    if (plan->pairs.grid != 0) {
+        const GemmParams g = prepare(plan->pairs);
+        cudaError_t err = launch_dependent(grouped_gemm_kernel<kRaw, true>, plan->pairs.grid, kGemmThreads,
+                                           plan->pairs.smem, s, g, dependent, 2);
+        if (err != cudaSuccess) return err;
+        dependent = true;
+    }
+    const GemmParams g = prepare(plan->single);
+    return launch_dependent(grouped_gemm_kernel<kRaw, false>, plan->single.grid, kGemmThreads, plan->single.smem, s, g,
                             dependent);
+}
+
+extern "C" int gcmoe_kernels_per_launch(const gcmoe_plan* plan) {
+    return plan == nullptr ? 0 : (plan->pairs.grid != 0 ? 4 : 3);
 }
 
 extern "C" int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned mask, void* cuda_stream) {
@@ -593,12 +627,12 @@ extern "C" int gcmoe_launch_kernels(gcmoe_plan* plan, unsigned mask, void* cuda_
         chained = true;
     }
     if (mask & 6u) {
-        // both GEMMs of the layer are one launch; either one alone is for tests and timing
-        GemmParams g = (mask & 6u) == 6u ? plan->fused : (mask & 2u) ? plan->up : plan->down;
-        // Launched together with the call's dispatch kernel the GEMMs start while it runs and
-        // wait for its tables; launched alone they find the tables of the last call in place.
-        g.wait_tables = chained ? 1u : 0u;
-        GCMOE_CUDA(launch_gemm<false>(plan, g, s, chained));
+        // both GEMMs of the layer are one launch (per regime); either one alone is for tests and timing
+        const unsigned which = mask & 6u;
+        auto pick = [which](const gcmoe::Plan::Regime& r) -> const GemmParams& {
+            return which == 6u ? r.fused : which == 2u ? r.up : r.down;
+        };
+        GCMOE_CUDA(launch_gemms<false>(plan, pick, s, chained, chained, nullptr));
         chained = true;
     } else chained = false;
     if (mask & 8u)
@@ -691,12 +725,9 @@ extern "C" int gcmoe_stage_inputs(const gcmoe_stage_args* args, void* cuda_strea
 
 extern "C" int gcmoe_debug_gemm_l1_raw(gcmoe_plan* plan, uint64_t out, void* cuda_stream) {
     if (plan == nullptr || out == 0) return fail(GCMOE_ERR_INVALID, "null argument");
-    GemmParams g = plan->up;
-    g.seg[0] = plan->up.seg[plan->up.num_segments - 1];   // the routed gate/up segment alone
-    g.num_segments = 1;
-    g.raw_out = reinterpret_cast<float*>(out);
-    g.wait_tables = 0;
-    GCMOE_CUDA(launch_gemm<true>(plan, g, static_cast<cudaStream_t>(cuda_stream), false));
+    auto pick = [](const gcmoe::Plan::Regime& r) -> const GemmParams& { return r.up; };
+    GCMOE_CUDA(launch_gemms<true>(plan, pick, static_cast<cudaStream_t>(cuda_stream), false, false,
+                                  reinterpret_cast<float*>(out)));
     GCMOE_CUDA(cudaGetLastError());
     return GCMOE_OK;
 }
@@ -773,7 +804,7 @@ extern "C" int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const g
     // cursor), whose place depends on the geometry.  The rest is rewritten by the dispatch kernel.
     cudaError_t err = cudaMemsetAsync(scratch, 0, kStatusWords * 4, s);
     if (err == cudaSuccess)
-        err = cudaMemsetAsync(const_cast<uint32_t*>(plan->fused.call_info), 0, kCallInfoWords * sizeof(uint32_t), s);
+        err = cudaMemsetAsync(const_cast<uint32_t*>(plan->single.fused.call_info), 0, kCallInfoWords * sizeof(uint32_t), s);
     int rc = err == cudaSuccess ? gcmoe_launch(plan, cuda_stream)
                                 : fail(GCMOE_ERR_CUDA, "cudaMemsetAsync failed: %s", cudaGetErrorString(err));
     if (rc == GCMOE_OK) {
@@ -782,7 +813,7 @@ extern "C" int gcmoe_launch_static_scratch(const gcmoe_problem* problem, const g
         std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
         int device = 0;
         if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < kMaxDevices)
-            g_static_last_failed_word[device] = plan->fused.failed;
+            g_static_last_failed_word[device] = plan->single.fused.failed;
     }
     gcmoe_plan_destroy(plan);   // host object only; the enqueued kernels carry their parameters by value
     return rc;

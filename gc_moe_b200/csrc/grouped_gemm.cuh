@@ -106,7 +106,7 @@ struct GemmSegment {
     const int* count;        // [experts] rows per expert
     const int* row_start;    // [experts] first row of the expert in the activation tensor
     const int* sf_start;     // [experts] first scale row of the expert's tiles in act_sf (and out_sf_private)
-    uint32_t tile_rows;      // rows per tile of every expert, or 0: expert_tile_rows(ref_block_m, rows of the expert)
+    uint32_t tile_rows;      // rows per tile of every expert, or 0: expert_tile_rows(regime, rows of the expert)
     uint32_t act_sf_stride;  // words between consecutive K128 planes of act_sf
     uint32_t w_sf_stride;    // words between consecutive planes of w_sf
     uint32_t w_sf_kblocks;   // K128 blocks one w_sf word covers: 1 (K32 scales) or 4 (K128 scales)
@@ -159,6 +159,7 @@ struct GemmParams {
     const uint32_t* call_info;        // [kCallInfoWords] written by the dispatch kernel
     const uint32_t* epoch_word;       // the workspace's call counter (recv_parity)
     uint32_t wait_tables;             // 1: launched with the call's dispatch kernel, wait for its tables
+    uint32_t dual_regime;             // 1: both regimes' launches are enqueued, call_info says which one works
     const uint32_t* rows_arrived;     // this rank's exchange::kRowsArrived, [2][kMaxLocalExperts]
     uint32_t* failed;                 // this rank's exchange::kFailed
     uint64_t combine_arrived[kMaxRanks];  // address of exchange::kCombineArrived on each rank
@@ -318,6 +319,31 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     ctl.kernel = kKernelGemmL1;
     if constexpr (kPair) ctl.peer_abort = ptx::mapa(ptx::smem_u32(const_cast<uint32_t*>(abort_word)), cta ^ 1u);
 
+    if constexpr (!kPair) {
+        // Both regimes' launches are enqueued, the pair one first.  When the dispatch kernel has
+        // already published its choice and it is the pair regime, this launch has nothing to do:
+        // leave before setting anything up.  (The pair launch cannot take this shortcut CTA by
+        // CTA -- the two CTAs of a cluster must take the same path -- and does not need to: its
+        // set-up overlaps the dispatch kernel.)
+        if (p.dual_regime != 0u) {
+            volatile uint32_t& not_mine = *reinterpret_cast<volatile uint32_t*>(smem_raw);   // stage memory, not in use yet
+            if (threadIdx.x == 0) {
+                uint32_t ready = 1;
+                if (p.wait_tables != 0u) {
+                    uint32_t v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.call_info + kCallTablesReady) : "memory");
+                    ready = v == *reinterpret_cast<const volatile uint32_t*>(p.epoch_word) + 1u;
+                }
+                not_mine = ready != 0u && *reinterpret_cast<const volatile uint32_t*>(p.call_info + kCallPairRegime) != 0u;
+            }
+            __syncthreads();
+            if (not_mine != 0u) {
+                if (threadIdx.x == 0) ptx::grid_dependency_wait();   // retire after the launches before this one
+                return;
+            }
+            __syncthreads();      // everyone has read the word before the set-up below reuses the memory
+        }
+    }
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < p.stages; ++s) {
             // stage filled: both producers (of both CTAs of a pair); stage free: the
@@ -410,7 +436,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
     const uint32_t bm = p.block_m;
     // nothing to do once a wait on this workspace has given up
-    const uint32_t total_tiles = (*reinterpret_cast<const volatile uint32_t*>(p.failed) != 0u || *abort_word != 0u)
+    // ... and nothing when the dispatch kernel chose the other regime for this call
+    const bool mine = !p.dual_regime || (p.call_info[kCallPairRegime] != 0u) == kPair;
+    const uint32_t total_tiles = (!mine || *reinterpret_cast<const volatile uint32_t*>(p.failed) != 0u || *abort_word != 0u)
                                      ? 0u : seg_meta[4 + kMaxSegments];
     const uint32_t generation = p.call_info[kCallGeneration];
 
@@ -434,7 +462,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         c.expert = lo;
         const uint32_t rows = static_cast<uint32_t>(start[ne + 1 + lo]);
         const uint32_t tn = p.seg[c.seg].tile_rows != 0u ? p.seg[c.seg].tile_rows
-                                                         : expert_tile_rows(p.seg[c.seg].ref_block_m, rows);
+                                                         : expert_tile_rows(kPair, rows);
         const uint32_t t = c.block - static_cast<uint32_t>(start[lo]);
         const uint32_t left = rows - t * tn;
         c.valid = left < tn ? left : tn;
