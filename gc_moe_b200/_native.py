@@ -21,7 +21,7 @@ class Problem(ctypes.Structure):
         'intermediate', 'num_tokens', 'block_m', 'ring_tokens', 'sf_ring_tokens',
         'num_shared_experts', 'shared_gran_k', 'has_clamp')] + [
         ('clamp', ctypes.c_float)] + [(name, ctypes.c_int32) for name in (
-            'fast_math', 'timeout_ms', 'num_sms')]
+            'fast_math', 'timeout_ms', 'num_sms', 'dispatch_sms')]
 
 
 class Buffers(ctypes.Structure):

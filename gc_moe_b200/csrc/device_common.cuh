@@ -145,17 +145,19 @@ constexpr uint32_t kCountsReady = 0;        // u32 [2][kMaxRanks]: epoch+1 once 
 constexpr uint32_t kSourceBlockM = 1024;    // u32 [2][kMaxRanks]: block-M each rank uses for its pool
 constexpr uint32_t kFailed = 1920;          // u32: a bounded wait of some call on this workspace ran out
 constexpr uint32_t kCombineArrived = 2048;  // u32 [2] (128 bytes apart): rows x tiles landed in combine_tokens
-constexpr uint32_t kRowsArrived = 4096;     // u32 [2][kMaxLocalExperts]: dispatched rows landed per local expert
+constexpr uint32_t kTilesUsed = 1928;       // u32 [2]: row tiles of the last call of each generation (how many counters to clear)
 constexpr uint32_t kCounts = 8192;          // u32 [2][P][E]: routes of source s to global expert e
+constexpr uint32_t kMaxRowTiles = 1u << 18;
+constexpr uint32_t kTileArrived = 2u << 20; // u32 [2][kMaxRowTiles]: dispatched rows landed per GEMM row tile of this rank
 // every field ends before the next one begins, for the largest group the API admits
 static_assert(kCountsReady + 2u * kMaxRanks * 4u <= kSourceBlockM, "kCountsReady overlaps kSourceBlockM");
 static_assert(kSourceBlockM + 2u * kMaxRanks * 4u <= kFailed, "kSourceBlockM overlaps kFailed");
-static_assert(kFailed + 4u <= kCombineArrived, "kFailed overlaps kCombineArrived");
-static_assert(kCombineArrived + 128u + 4u <= kRowsArrived, "kCombineArrived overlaps kRowsArrived");
-static_assert(kRowsArrived + 2u * kMaxLocalExperts * 4u <= kCounts, "kRowsArrived overlaps kCounts");
-__host__ __device__ __forceinline__ uint32_t bytes(uint32_t ranks, uint32_t experts) {
-    return kCounts + 2u * ranks * experts * 4u;
-}
+static_assert(kFailed + 4u <= kTilesUsed, "kFailed overlaps kTilesUsed");
+static_assert(kTilesUsed + 8u <= kCombineArrived, "kTilesUsed overlaps kCombineArrived");
+static_assert(kCombineArrived + 128u + 4u <= kCounts, "kCombineArrived overlaps kCounts");
+static_assert(kCounts + 2u * kMaxRanks * kMaxExperts * 4u <= kTileArrived, "kCounts overlaps kTileArrived");
+constexpr uint32_t kBytes = kTileArrived + 2u * kMaxRowTiles * 4u;   // 4 MiB of the 8 MiB region
+static_assert(kBytes <= (8u << 20), "exchange block exceeds the signal region it lives in");
 }  // namespace exchange
 
 // Two regimes of the expert GEMMs:

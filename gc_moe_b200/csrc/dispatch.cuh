@@ -282,11 +282,17 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         {
             // Counters of the NEXT call's generation start from zero; nobody can be
             // adding to them yet (a peer reaches its next call only after this
-            // rank has finished the current one).
+            // rank has finished the current one).  The last call of that generation
+            // left as many row-tile counters dirty as it had row tiles.
             uint8_t* const ex = my_arena + p.off_exchange;
-            uint32_t* const arrived_next = reinterpret_cast<uint32_t*>(ex + exchange::kRowsArrived) + (gen ^ 1u) * kMaxLocalExperts;
-            for (uint32_t l = tid; l < EL; l += kDispatchThreads) arrived_next[l] = 0;
-            if (tid == 0) *reinterpret_cast<uint32_t*>(ex + exchange::kCombineArrived + (gen ^ 1u) * 128) = 0;
+            uint32_t* const used = reinterpret_cast<uint32_t*>(ex + exchange::kTilesUsed);
+            uint32_t* const arrived_next = reinterpret_cast<uint32_t*>(ex + exchange::kTileArrived) + (gen ^ 1u) * exchange::kMaxRowTiles;
+            const uint32_t dirty = used[gen ^ 1u];
+            for (uint32_t i = tid; i < dirty; i += kDispatchThreads) arrived_next[i] = 0;
+            if (tid == 0) {
+                used[gen] = misc[3];
+                *reinterpret_cast<uint32_t*>(ex + exchange::kCombineArrived + (gen ^ 1u) * 128) = 0;
+            }
         }
         if (tid == 0) {
             p.expert_block_start[EL] = static_cast<int>(misc[1]);
@@ -398,12 +404,12 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             if (tile_ordered) sf_dst[static_cast<size_t>(w) * p.sf_ring + tile_row] = word;
         }
         // Tell the owner's GEMM launch (which may already be running, on this GPU too)
-        // that one more row of the expert has landed: a release, cumulative over the
-        // warp's stores ordered by __syncwarp.
+        // that one more row of this GEMM row tile has landed: a release, cumulative over
+        // the warp's stores ordered by __syncwarp.
         __syncwarp();
         if (lane == 0) {
-            uint32_t* const arrived = reinterpret_cast<uint32_t*>(dst_arena + p.off_exchange + exchange::kRowsArrived) +
-                                      gen * kMaxLocalExperts + (e - owner * EL);
+            uint32_t* const arrived = reinterpret_cast<uint32_t*>(dst_arena + p.off_exchange + exchange::kTileArrived) +
+                                      gen * exchange::kMaxRowTiles + first_tile[e] + pos / tn;
             if (P > 1) ptx::red_release_sys_add(arrived, 1u);
             else asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(arrived), "r"(1u) : "memory");
         }

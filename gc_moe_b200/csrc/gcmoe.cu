@@ -126,6 +126,7 @@ static int check_problem(const gcmoe_problem& q) {
     const long long routes = 1ll * q.num_ranks * q.capacity * (q.topk < local ? q.topk : local);
     if (q.ring_tokens < routes + local * (bm - 1))
         return fail(GCMOE_ERR_UNSUPPORTED, "ring of %d rows cannot hold the whole receive pool", q.ring_tokens);
+    if (q.dispatch_sms < 0) return fail(GCMOE_ERR_INVALID, "invalid dispatch SM request");
     if (q.num_shared_experts < 0 || (q.num_shared_experts > 0 && q.shared_gran_k != 32 && q.shared_gran_k != 128))
         return fail(GCMOE_ERR_INVALID, "invalid shared expert configuration");
     if (1ll * q.num_shared_experts * q.intermediate > 65536)
@@ -175,9 +176,10 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     for (int r = 0; r < q.num_ranks; ++r)
         if (b.arena_base[r] == 0 || b.arena_base[r] % 16)
             return fail(GCMOE_ERR_INVALID, "arena of rank %d is not mapped", r);
-    if (b.off_exchange == 0 || b.off_exchange % 128 || exchange::bytes(q.num_ranks, q.num_experts) > (8u << 20))
-        return fail(GCMOE_ERR_INVALID, "exchange block missing or too small for %d ranks x %d experts",
-                    q.num_ranks, q.num_experts);
+    if (b.off_exchange == 0 || b.off_exchange % 128)
+        return fail(GCMOE_ERR_INVALID, "exchange block missing or misaligned");
+    if (uint64_t(q.ring_tokens) / 16 + uint64_t(q.num_experts / q.num_ranks) + 1 > exchange::kMaxRowTiles)
+        return fail(GCMOE_ERR_UNSUPPORTED, "ring of %d rows has more row tiles than the arrival counters hold", q.ring_tokens);
 
     GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     GCMOE_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
@@ -258,7 +260,15 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
     d.block_m = bm; d.sf_ring = q.sf_ring_tokens;
     const uint32_t routes = uint32_t(q.num_tokens) * q.topk;
     const uint32_t warps = kDispatchThreads / 32;
+    // One warp pushes one route at a time.  The grid is kept small (32 CTAs unless the caller
+    // says otherwise): the expert GEMMs start while this kernel runs and need the other SMs
+    // (a GEMM CTA fills an SM's shared memory, so it cannot share an SM with a dispatch CTA),
+    // and the pushes are bound by NVLink, not by the number of warps.  With several ranks at
+    // least one CTA per peer, so that the counts reach all peers at the same time.
+    const uint32_t dcap = q.dispatch_sms > 0 ? uint32_t(q.dispatch_sms) : 32u;
     uint32_t dgrid = (routes + warps - 1) / warps;
+    if (P > 1 && dgrid < P) dgrid = P;
+    if (dgrid > dcap) dgrid = dcap;
     dgrid = dgrid < 1 ? 1 : (dgrid > uint32_t(plan->num_sms) ? plan->num_sms : dgrid);
     plan->dispatch_grid = dgrid;
     plan->dispatch_smem = dispatch_smem_bytes(E, P, (routes + dgrid - 1) / dgrid);
@@ -314,7 +324,7 @@ extern "C" int gcmoe_plan_create(const gcmoe_problem* problem, const gcmoe_buffe
         g.dual_regime = dual ? 1u : 0u;
         g.epoch_word = reinterpret_cast<const uint32_t*>(arena + b.off_recv_parity);
         g.tile_cursor = call_info + (pair ? kCallTileCursorPair : kCallTileCursor);
-        g.rows_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kRowsArrived);
+        g.tile_arrived = reinterpret_cast<const uint32_t*>(arena + b.off_exchange + exchange::kTileArrived);
         g.failed = reinterpret_cast<uint32_t*>(arena + b.off_exchange + exchange::kFailed);
         for (uint32_t r = 0; r < P; ++r) {
             g.combine_arrived[r] = b.arena_base[r] + b.off_exchange + exchange::kCombineArrived;

@@ -46,9 +46,9 @@
 //
 // The launch starts while the dispatch kernel of the same call is still running
 // (programmatic dependent launch, no griddepcontrol.wait in front): it waits for
-// the call's tables (a release by dispatch CTA 0), then per expert for the rows
+// the call's tables (a release by dispatch CTA 0), then per row tile for the rows
 // pushed into the pool (arrival counters, this GPU's own dispatch included), so
-// the weight stream of the first experts overlaps the exchange.
+// the weight stream and the first tiles of every expert overlap the exchange.
 //
 // Replaces the reference's role-2 compute kernel
 // (gc_moe/impls/sm100_fp8_fp4_gc_moe.py:1108-1905) and its device scheduler
@@ -160,7 +160,7 @@ struct GemmParams {
     const uint32_t* epoch_word;       // the workspace's call counter (recv_parity)
     uint32_t wait_tables;             // 1: launched with the call's dispatch kernel, wait for its tables
     uint32_t dual_regime;             // 1: both regimes' launches are enqueued, call_info says which one works
-    const uint32_t* rows_arrived;     // this rank's exchange::kRowsArrived, [2][kMaxLocalExperts]
+    const uint32_t* tile_arrived;     // this rank's exchange::kTileArrived, [2][kMaxRowTiles]: rows landed per row tile
     uint32_t* failed;                 // this rank's exchange::kFailed
     uint64_t combine_arrived[kMaxRanks];  // address of exchange::kCombineArrived on each rank
     uint32_t num_ranks;
@@ -524,7 +524,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         // ------------------------------------------------------------ producers
         const bool weights = warp == 0;
         StageCursor cur;
-        uint32_t armed = 0, armed_parity = 0, ntiles = 0, ready_expert = 0xFFFFFFFFu;
+        uint32_t armed = 0, armed_parity = 0, ntiles = 0, ready_block = 0xFFFFFFFFu;
         bool ok = true;
         for (; ok; ++ntiles) {
             if (weights && lane == 0) *feed_pos = ntiles + 1;     // lets the scheduler claim the tile after this one
@@ -556,17 +556,16 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             const uint32_t act_row0 = tc.row0 + (kPair ? cta * (n_cols / 2) : 0u);
             // An expert with several row tiles streams its weights once per tile: keep them in L2.
             const uint64_t w_hint = tc.tiles_of_expert >= 2u ? ptx::kEvictNormal : ptx::kEvictFirst;
-            if (!weights && sg.kind == kSegUp && !sg.shared && e != ready_expert) {
-                // The rows of this expert are pushed by the dispatch kernels (of this and
-                // the other GPUs): wait until all of them have landed, then order the TMA
-                // (async proxy) after the acquire.
+            if (!weights && sg.kind == kSegUp && !sg.shared && tc.block != ready_block) {
+                // The rows of this tile are pushed by the dispatch kernels (of this and the
+                // other GPUs), which count them per row tile: wait until all of them have
+                // landed, then order the TMA (async proxy) after the acquire.
                 uint32_t landed = 1;
                 if (lane == 0)
-                    landed = flag_wait_eq(p.rows_arrived + generation * kMaxLocalExperts + e,
-                                          rows_of_expert(tc.seg, e), ctl, 5);
+                    landed = flag_wait_eq(p.tile_arrived + generation * exchange::kMaxRowTiles + tc.block, tc.valid, ctl, 5);
                 if (!__shfl_sync(0xffffffffu, landed, 0)) { ok = false; break; }
                 ptx::fence_proxy_async_global();
-                ready_expert = e;
+                ready_block = tc.block;
             }
             if (!weights && sg.kind == kSegDown && sg.done_target != 0) {
                 // The tile's intermediate rows are written by the up tiles of this same
@@ -789,7 +788,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         uint32_t xbuf = 0;
         bool ok = true;
         const float clamp_bf16 = __bfloat162float(__float2bfloat16_rn(p.clamp));
-        uint32_t rows_ready = 0xFFFFFFFFu;   // expert whose pushed rows, weights and metadata are known to have landed
+        uint32_t rows_ready = 0xFFFFFFFFu;   // routed row tile whose pushed rows, weights and metadata are known to have landed
         for (uint32_t i = etid; i < kMaxRanks; i += 128) arrive[i] = 0;
         epilogue_barrier();
         for (; ok; ++it) {
@@ -809,17 +808,15 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             // Stage what the stores need to know about the tile's rows while the
             // main loop is still running: route weight (gate/up) or destination.
             uint32_t* const info = row_info + (it & 1u) * bm * 4;
-            if (!kRaw && !sg.shared && e != rows_ready) {
+            if (!kRaw && !sg.shared && b != rows_ready) {
                 // Route weights and source metadata are pushed together with the rows by
-                // the dispatch kernels; wait until the expert's rows have all landed
-                // (a down tile can be reached before its gate/up tiles were waited for
-                // by this CTA).
+                // the dispatch kernels; wait until the tile's rows have all landed (a down
+                // tile can be reached before its gate/up tiles were waited for by this CTA).
                 bool landed = true;
                 if (etid == 0)
-                    landed = flag_wait_eq(p.rows_arrived + generation * kMaxLocalExperts + e,
-                                          rows_of_expert(tc.seg, e), ctl, 6);
+                    landed = flag_wait_eq(p.tile_arrived + generation * exchange::kMaxRowTiles + b, valid, ctl, 6);
                 if (!all_epilogue_threads(landed)) { ok = false; break; }
-                rows_ready = e;
+                rows_ready = b;
             }
             if (kRaw) {
             } else if (sg.kind == kSegUp) {

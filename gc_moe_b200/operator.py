@@ -57,6 +57,28 @@ def _timeout_ms() -> int:
     return min(seconds * 1000, 2_000_000_000)
 
 
+def _dispatch_sms() -> int:
+    """Upper bound of the SMs the dispatch kernel occupies (0 = the library's default
+    of 32).  GC_MOE_DISPATCH_SMS is parsed as the reference parses it: a signed decimal
+    int32 without whitespace (gc_moe/runtime/gc_moe.py:29-49); a request outside
+    [2, SM count) is refused like the reference's SM split refuses it
+    (gc_moe/runtime/gc_moe.py:92-93)."""
+    import re
+    name = 'GC_MOE_DISPATCH_SMS'
+    raw = os.environ.get(name)
+    if raw is None:
+        return 0
+    if re.fullmatch(r'-?[0-9]+', raw) is None:
+        raise ValueError(f'invalid value for {name}: {raw}')
+    value = int(raw)
+    if not -(1 << 31) <= value < (1 << 31):
+        raise ValueError(f'invalid value for {name}: {raw}')
+    total = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    if not 2 <= value < total:
+        raise ValueError('invalid dispatch SM request')
+    return value
+
+
 def _build_plan(config: ValidatedCall, y, l1_weights, l2_weights, call_buffer,
                 shared_l1, shared_l2, stats) -> _Plan:
     lib = _native.library()
@@ -70,7 +92,8 @@ def _build_plan(config: ValidatedCall, y, l1_weights, l2_weights, call_buffer,
         num_shared_experts=config.shared_experts, shared_gran_k=config.shared_weight_gran_k,
         has_clamp=int(math.isfinite(config.clamp)),
         clamp=config.clamp if math.isfinite(config.clamp) else 0.0,
-        fast_math=int(config.fast_math), timeout_ms=_timeout_ms(), num_sms=0)
+        fast_math=int(config.fast_math), timeout_ms=_timeout_ms(), num_sms=0,
+        dispatch_sms=_dispatch_sms())
     scratch = torch.zeros(lib.gcmoe_scratch_bytes(ctypes.byref(prob)), dtype=torch.uint8,
                           device=y.device)
     buf = _native.Buffers()
@@ -113,7 +136,8 @@ def _build_plan(config: ValidatedCall, y, l1_weights, l2_weights, call_buffer,
 def _plan_key(config: ValidatedCall, y, l1_weights, l2_weights, shared_l1, shared_l2, stats):
     tensors = [y, *l1_weights, *l2_weights, *(shared_l1 or ()), *(shared_l2 or ())]
     return (config, tuple(t.data_ptr() for t in tensors),
-            stats.data_ptr() if stats is not None else 0, _timeout_ms())
+            stats.data_ptr() if stats is not None else 0, _timeout_ms(),
+            os.environ.get('GC_MOE_DISPATCH_SMS'))
 
 
 def _capturing() -> bool:
