@@ -47,6 +47,15 @@ class StageArgs(ctypes.Structure):
             'shared_sf_rows', 'block_m', 'num_tokens', 'hidden', 'num_experts', 'topk')]
 
 
+class TransformArgs(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_uint64) for name in (
+        'payload_in', 'payload_out', 'sf_in', 'sf_out', 'block_codes',
+        'sf_in_stride_g', 'sf_in_stride_r', 'sf_in_stride_p',
+        'sf_out_stride_g', 'sf_out_stride_r', 'sf_out_stride_p')] + [(name, ctypes.c_uint32) for name in (
+            'groups', 'rows', 'row_bytes', 'segment_bytes', 'sf_packs', 'k_blocks', 'interleave_gate_up',
+            'reserved')]
+
+
 # GC_MOE_B200_LIBRARY points at another build of the same library (a tuning variant).
 LIBRARY_PATH = os.environ.get('GC_MOE_B200_LIBRARY') or os.path.join(
     os.path.dirname(os.path.abspath(__file__)), 'libgcmoe_sm100.so')
@@ -65,6 +74,7 @@ _SIGNATURES = {
     'gcmoe_status_read': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p,
                                          ctypes.POINTER(ctypes.c_uint32)]),
     'gcmoe_stage_inputs': (ctypes.c_int, [ctypes.POINTER(StageArgs), ctypes.c_void_p]),
+    'gcmoe_transform_weights': (ctypes.c_int, [ctypes.POINTER(TransformArgs), ctypes.c_void_p]),
     'gcmoe_launch_static_scratch': (ctypes.c_int, [ctypes.POINTER(Problem), ctypes.POINTER(Buffers), ctypes.c_void_p]),
     'gcmoe_static_scratch_status': (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_uint32)]),
     'gcmoe_debug_expire_wait': (ctypes.c_int, [ctypes.c_void_p, ctypes.c_uint, ctypes.c_void_p]),

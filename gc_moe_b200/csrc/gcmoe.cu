@@ -9,6 +9,7 @@
 #include "../../include/gcmoe.h"
 #include "combine.cuh"
 #include "stage_inputs.cuh"
+#include "transform_weights.cuh"
 #include "dispatch.cuh"
 #include "grouped_gemm.cuh"
 
@@ -729,6 +730,46 @@ extern "C" int gcmoe_stage_inputs(const gcmoe_stage_args* args, void* cuda_strea
     p.hidden = a.hidden; p.num_experts = a.num_experts; p.topk = a.topk;
     const size_t smem = a.router_logits != 0 ? size_t(a.num_experts) * 4 : 0;
     stage_inputs_kernel<<<a.num_tokens, kStageThreads, smem, static_cast<cudaStream_t>(cuda_stream)>>>(p);
+    GCMOE_CUDA(cudaGetLastError());
+    return GCMOE_OK;
+}
+
+extern "C" int gcmoe_transform_weights(const gcmoe_transform_args* args, void* cuda_stream) {
+    if (args == nullptr) return fail(GCMOE_ERR_INVALID, "null argument");
+    const gcmoe_transform_args& a = *args;
+    if (a.groups == 0 || a.rows == 0 || a.row_bytes == 0) return GCMOE_OK;
+    if ((a.segment_bytes != 64 && a.segment_bytes != 128) || a.row_bytes % a.segment_bytes)
+        return fail(GCMOE_ERR_INVALID, "weight rows must hold whole K128 segments of 64 (FP4) or 128 (FP8) bytes");
+    if (a.payload_in == 0 || a.payload_out == 0 || a.payload_in % 16 || a.payload_out % 16)
+        return fail(GCMOE_ERR_INVALID, "weight payload missing or not 16-byte aligned");
+    if (a.interleave_gate_up && a.rows % 16) return fail(GCMOE_ERR_INVALID, "W1 rows must be a multiple of 16");
+    if (a.sf_out != 0) {
+        if (a.rows % 128 || a.sf_packs == 0 || a.sf_out % 4)
+            return fail(GCMOE_ERR_INVALID, "scale rows must be a multiple of 128 and the words 4-byte aligned");
+        if (a.block_codes == 0 && (a.sf_in == 0 || a.sf_in % 4))
+            return fail(GCMOE_ERR_INVALID, "neither scale words nor block codes given");
+        if (a.block_codes != 0 && (a.groups != 1 || a.k_blocks == 0 || a.sf_packs != (a.k_blocks + 3) / 4))
+            return fail(GCMOE_ERR_INVALID, "block codes need one matrix and ceil(k_blocks / 4) words per row");
+    }
+    TransformParams p = {};
+    p.payload_in = reinterpret_cast<const uint4*>(a.payload_in);
+    p.payload_out = reinterpret_cast<uint4*>(a.payload_out);
+    p.sf_in = reinterpret_cast<const uint32_t*>(a.sf_in);
+    p.sf_out = reinterpret_cast<uint32_t*>(a.sf_out);
+    p.block_codes = reinterpret_cast<const uint8_t*>(a.block_codes);
+    p.groups = a.groups; p.rows = a.rows; p.row_vecs = a.row_bytes / 16; p.seg_vecs = a.segment_bytes / 16;
+    p.sf_packs = a.sf_packs; p.k_blocks = a.k_blocks;
+    p.in_stride_g = a.sf_in_stride_g; p.in_stride_r = a.sf_in_stride_r; p.in_stride_p = a.sf_in_stride_p;
+    p.out_stride_g = a.sf_out_stride_g; p.out_stride_r = a.sf_out_stride_r; p.out_stride_p = a.sf_out_stride_p;
+    p.interleave = a.interleave_gate_up;
+    cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+    auto blocks = [](uint64_t items) {
+        const uint64_t b = (items + kTransformThreads - 1) / kTransformThreads;
+        return unsigned(b < 1 ? 1 : (b > 148ull * 16 ? 148ull * 16 : b));
+    };
+    transform_payload_kernel<<<blocks(uint64_t(a.groups) * a.rows * p.row_vecs), kTransformThreads, 0, s>>>(p);
+    if (a.sf_out != 0)
+        transform_scales_kernel<<<blocks(uint64_t(a.groups) * a.rows * a.sf_packs), kTransformThreads, 0, s>>>(p);
     GCMOE_CUDA(cudaGetLastError());
     return GCMOE_OK;
 }

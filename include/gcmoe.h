@@ -186,6 +186,33 @@ typedef struct gcmoe_stage_args {
  * Allocates nothing; capturable. */
 int gcmoe_stage_inputs(const gcmoe_stage_args* args, void* cuda_stream);
 
+/* One weight matrix (or one stack of per-expert matrices) of
+ * gcmoe_transform_weights: device addresses and element counts. */
+typedef struct gcmoe_transform_args {
+    uint64_t payload_in;      /* [groups][rows][row_bytes]: packed FP4 int8 [E][rows][K/2]
+                               * or FP8 [rows][K] (groups = 1)                          */
+    uint64_t payload_out;     /* [groups][row_bytes / segment_bytes][rows][segment_bytes] */
+    uint64_t sf_in;           /* int32 packed scale words [groups][rows][sf_packs] with the
+                               * element strides below, or 0 when block_codes is given */
+    uint64_t sf_out;          /* same shape, strides below                             */
+    uint64_t block_codes;     /* uint8 [rows / 128][k_blocks]: one UE8M0 byte per
+                               * 128 x 128 block, expanded on the fly; or 0           */
+    uint64_t sf_in_stride_g, sf_in_stride_r, sf_in_stride_p;     /* in elements */
+    uint64_t sf_out_stride_g, sf_out_stride_r, sf_out_stride_p;
+    uint32_t groups, rows, row_bytes, segment_bytes;   /* segment: 64 (FP4) or 128 (FP8) */
+    uint32_t sf_packs, k_blocks;
+    uint32_t interleave_gate_up;   /* 1 for W1: rows [gate ; up] -> groups of 8 + 8   */
+    uint32_t reserved;
+} gcmoe_transform_args;
+
+/* Re-layout one weight set for the kernels, two launches on `cuda_stream`: the
+ * K128 tile repack of the payload, and the scale words' row interleave and 4 x 32
+ * transpose (with the block-row expansion of 128 x 128 scales when block_codes is
+ * given).  Produces the bytes of transform_weights_for_gc_moe
+ * (gc_moe/gc/__init__.py:166-223; gc_moe/jit_kernels/impls/runtime_utils.py:86-118).
+ * Allocates nothing; input and output must not overlap. */
+int gcmoe_transform_weights(const gcmoe_transform_args* args, void* cuda_stream);
+
 /* One layer call for callers that cannot allocate device memory (no
  * counterpart in the reference, whose launch path allocates through its JIT
  * and graph caches).  Meant for hosts with a frozen device heap -- a serving
