@@ -73,11 +73,10 @@ struct DispatchParams {
 // Dynamic shared memory: seven u32 per expert (own count, own routes before the
 // slice, total over sources, routes of lower sources, first pool block, first
 // GEMM tile, first tile-ordered scale row), one block-M and one GEMM regime per rank,
-// then the CTA's slice: expert id, pool row, position inside the expert per route, and the
-// order in which the routes are pushed.
+// then the CTA's slice: expert id, pool row and position inside the expert per route.
 __host__ __device__ inline uint32_t dispatch_smem_bytes(uint32_t num_experts, uint32_t num_ranks,
                                                         uint32_t slice) {
-    return (7 * num_experts + 2 * num_ranks + 8 + 4 * slice) * 4;
+    return (7 * num_experts + 2 * num_ranks + 8 + 3 * slice) * 4;
 }
 
 __global__ void __launch_bounds__(kDispatchThreads)
@@ -100,7 +99,6 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     int* const slice_expert = reinterpret_cast<int*>(misc + 8);
     uint32_t* const slice_row = reinterpret_cast<uint32_t*>(slice_expert + slice);
     uint32_t* const slice_pos = slice_row + slice;
-    uint32_t* const slice_order = slice_pos + slice;   // slice entries in push order
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     ptx::launch_dependents();
@@ -367,55 +365,13 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     }
     __syncthreads();
 
-    // Push order: by destination -- owners starting with this rank (so that the sources do
-    // not all load the same owner's NVLink at the same time), experts ascending inside an
-    // owner.  The owner's GEMM launch walks its experts in the same order and each of its
-    // tiles starts as soon as its own rows have landed, so rows sent in this order let the
-    // expert GEMMs overlap the exchange; in token order every tile would complete only when
-    // the whole exchange does.  A counting sort of the slice by (owner distance, expert);
-    // the order inside one expert does not matter (positions are fixed above).
-    uint32_t* const order_count = before;        // [E], free again: positions are computed
-    for (uint32_t e = tid; e < E; e += kDispatchThreads) order_count[e] = 0;
-    __syncthreads();
-    auto push_key = [&](uint32_t e) -> uint32_t {
-        const uint32_t owner = e / EL;
-        return ((owner + P - p.rank) % P) * EL + (e - owner * EL);
-    };
-    for (uint32_t j = tid; j < hi - lo; j += kDispatchThreads)
-        if (slice_row[j] != 0xFFFFFFFFu) atomicAdd(&order_count[push_key(static_cast<uint32_t>(slice_expert[j]))], 1u);
-    __syncthreads();
-    if (warp == 0) {
-        const uint32_t per_lane = (E + 31) / 32;
-        uint32_t sum = 0;
-        for (uint32_t i = 0; i < per_lane; ++i) {
-            const uint32_t k = lane * per_lane + i;
-            if (k < E) sum += order_count[k];
-        }
-        uint32_t incl = sum;
-        for (uint32_t d = 1; d < 32; d <<= 1) {
-            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += v;
-        }
-        uint32_t run = incl - sum;
-        for (uint32_t i = 0; i < per_lane; ++i) {
-            const uint32_t k = lane * per_lane + i;
-            if (k < E) { const uint32_t c = order_count[k]; order_count[k] = run; run += c; }
-        }
-        if (lane == 31) misc[5] = incl;          // valid routes of the slice
-    }
-    __syncthreads();
-    for (uint32_t j = tid; j < hi - lo; j += kDispatchThreads)
-        if (slice_row[j] != 0xFFFFFFFFu)
-            slice_order[atomicAdd(&order_count[push_key(static_cast<uint32_t>(slice_expert[j]))], 1u)] = j;
-    __syncthreads();
-
     // One warp per route: copy the FP8 row (16 bytes per lane per step), scatter
     // its packed scale words into the owner's MN-major scale ring, then tell the
-    // owner one more row of that GEMM row tile has landed.
+    // owner one more row of that expert has landed.
     const uint32_t row_vecs = p.hidden / 16, sf_words = p.hidden / 128;
-    for (uint32_t n = warp; n < misc[5]; n += kDispatchThreads / 32) {
-        const uint32_t a = lo + slice_order[n];
+    for (uint32_t a = lo + warp; a < hi; a += kDispatchThreads / 32) {
         const uint32_t row = slice_row[a - lo];
+        if (row == 0xFFFFFFFFu) continue;
         const uint32_t e = static_cast<uint32_t>(slice_expert[a - lo]);
         const uint32_t owner = e / EL;
         const uint32_t bm = bm_of[owner], sf_block = round_up_u32(bm, 128);
