@@ -833,15 +833,19 @@ class CpuReference:
 
     def step_us(self) -> float:
         """Mean scaled latency of a layer call over one pass of the sweep."""
-        total = 0.0
+        total, raw = 0.0, 0.0
         for xq, xsf, sub, wts, scale in self.calls:
             t0 = time.perf_counter()
             self.O.moe_layer([xq], [xsf], [sub], [wts], self.q1, self.c1, self.q2, self.c2, [16], clamp=10.0)
-            total += (time.perf_counter() - t0) * scale
+            dt = time.perf_counter() - t0
+            raw += dt
+            total += dt * scale
+        self.last_unscaled_us = raw / len(self.calls) * 1e6      # what the host cores actually ran
         return total / len(self.calls) * 1e6
 
     def describe(self, value: float) -> dict:
         return {'value': round(value, 1), 'unit': 'us', 'cores': self.cores, 'kind': 'port',
+                'unscaled_us_per_call_actually_run': round(getattr(self, 'last_unscaled_us', 0.0), 1),
                 'sample': f'per token count in {list(self.wl.sweep)} (tokens of all {self.wl.world} rank(s) in one '
                           f'process): the first 1/{self.fraction} of the active experts (dequantise, both matmuls, '
                           'epilogues, combine) is run and timed; the reported value is that time scaled by '

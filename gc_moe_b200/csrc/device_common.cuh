@@ -183,14 +183,8 @@ static_assert(kBytes <= (8u << 20), "exchange block exceeds the signal region it
 // with many rows costs as few passes over its weights as possible.  The scale
 // words of the tiles are kept a second time in tile order (the reference layout
 // orders them by pool block).
-#ifndef GCMOE_PAIR_MIN_BLOCK_M
-#define GCMOE_PAIR_MIN_BLOCK_M 64
-#endif
-#ifndef GCMOE_PAIR_TILE_ROWS
-#define GCMOE_PAIR_TILE_ROWS 240
-#endif
-constexpr uint32_t kPairMinBlockM = GCMOE_PAIR_MIN_BLOCK_M;
-constexpr uint32_t kPairTileRows = GCMOE_PAIR_TILE_ROWS;
+constexpr uint32_t kPairMinBlockM = 64;
+constexpr uint32_t kPairTileRows = 240;
 constexpr uint32_t kPairExpertRows = 128;
 constexpr uint32_t kSingleTileRows = 64;
 constexpr uint32_t kDualMinRoutes = 4096;
