@@ -183,15 +183,16 @@ static_assert(kBytes <= (8u << 20), "exchange block exceeds the signal region it
 // with many rows costs as few passes over its weights as possible.  The scale
 // words of the tiles are kept a second time in tile order (the reference layout
 // orders them by pool block).
-constexpr uint32_t kPairMinBlockM = 64;
+constexpr uint32_t kPairMinBlockM = 96;
 constexpr uint32_t kPairTileRows = 240;
 constexpr uint32_t kPairExpertRows = 128;
 constexpr uint32_t kSingleTileRows = 64;
 constexpr uint32_t kDualMinRoutes = 4096;
 // Whether a call enqueues the launches of both regimes (host; the flag travels to the other ranks
-// with the block-M): calls large enough for some expert to collect hundreds of rows -- block-M 64
+// with the block-M): calls large enough for some expert to collect hundreds of rows -- block-M 96
 // and above, or 4096 routes in the group (taking this rank's token count for every rank).  Below
-// that the second launch's few microseconds would not be earned back.
+// that the second launch's microseconds (about 10 when the launches run one after the other)
+// would not be earned back.
 __host__ __device__ __forceinline__ bool dual_regime_call(uint32_t block_m, uint64_t group_routes) {
     return block_m >= kPairMinBlockM || group_routes >= kDualMinRoutes;
 }

@@ -197,8 +197,10 @@ def test_raw_accumulators_of_both_tile_regimes(small, tokens, hot):
     """The FP32 accumulators of the gate/up GEMM, read straight from TMEM, against
     an FP32 matmul of the dequantised operands: a sharper check of the MMA,
     descriptor and scale plumbing than y.  40 tokens run one CTA per tile
-    (cta_group::1), 300 and 900 tokens CTA pairs (cta_group::2) -- with all routes
-    on two experts an expert spans several 240-token tiles."""
+    (cta_group::1, the only launch enqueued); for 300 evenly routed tokens both
+    regimes' launches are enqueued and the dispatch kernel chooses one CTA per tile
+    again (no expert reaches 128 rows); with 900 tokens all routed to two experts
+    it chooses CTA pairs (cta_group::2) and an expert spans several 240-token tiles."""
     import ctypes
     from gc_moe_b200 import _native, operator
     from gc_moe_b200.contract import validate_call
