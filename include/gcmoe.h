@@ -60,7 +60,7 @@ typedef struct gcmoe_problem {
     int32_t timeout_ms;         /* limit of every device-side wait (0 = 2000)   */
     int32_t num_sms;            /* SMs to use (0 = all of the device)           */
     int32_t dispatch_sms;       /* upper bound of the dispatch kernel's CTAs, one
-                                 * per SM (0 = 32).  The expert GEMMs start while
+                                 * per SM (0 = 32, more for calls with more than 8192 routes).  The expert GEMMs start while
                                  * the dispatch kernel runs and take the other
                                  * SMs at once: the SM split the reference makes
                                  * with green contexts and GC_MOE_DISPATCH_SMS
