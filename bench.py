@@ -51,6 +51,9 @@ import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+# Device-side waits give up after this long.  The library's default of 2 s is short when a rank
+# of a loaded 8-GPU box falls behind during set-up; nothing in the timed regions waits that long.
+os.environ.setdefault('GC_MOE_NVLINK_BARRIER_TIMEOUT_SECS', '10')
 
 import torch  # noqa: E402
 
@@ -890,14 +893,22 @@ def main() -> None:
     ap.add_argument('--large-token', action='store_true',
                     help='profiling aid: run the large-token leg even with --skip-baselines')
     args = ap.parse_args()
+    # Standard output carries the one JSON line and nothing else: libraries that write to file
+    # descriptor 1 themselves (NCCL prints its version there under NCCL_DEBUG=VERSION) are sent to
+    # standard error for the length of the run.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     failed = False
     if args.impl == 'ours':
         args.warmup = max(args.warmup, 3)
         line, failed = run_ours(args)
     else:
         line = run_reference(args)
+    sys.stdout.flush()
     if line is not None:
-        print(json.dumps(line))
+        os.write(json_fd, (json.dumps(line) + '\n').encode())
+    os.close(json_fd)
     import torch.distributed as dist
     if dist.is_initialized():
         dist.destroy_process_group()
