@@ -369,6 +369,21 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     // its packed scale words into the owner's MN-major scale ring, then tell the
     // owner one more row of that expert has landed.
     const uint32_t row_vecs = p.hidden / 16, sf_words = p.hidden / 128;
+    // Arrivals leave in batches of up to kArrivalBatch rows per warp: lane j keeps the counter of
+    // the j-th row of the batch, and one fence per lane covers the stores of all of them, so
+    // a warp with several rows waits for the round trip of its stores once per batch instead
+    // of once per row.
+    constexpr uint32_t kArrivalBatch = 4;
+    uint32_t* pending = nullptr;
+    uint32_t num_pending = 0;
+    auto flush_arrivals = [&]() {
+        __syncwarp();
+        if (lane < num_pending) {
+            if (P > 1) asm volatile("fence.acq_rel.sys;\n\tred.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(pending), "r"(1u) : "memory");
+            else asm volatile("fence.acq_rel.gpu;\n\tred.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(pending), "r"(1u) : "memory");
+        }
+        num_pending = 0;
+    };
     for (uint32_t a = lo + warp; a < hi; a += kDispatchThreads / 32) {
         const uint32_t row = slice_row[a - lo];
         if (row == 0xFFFFFFFFu) continue;
@@ -404,16 +419,14 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
             if (tile_ordered) sf_dst[static_cast<size_t>(w) * p.sf_ring + tile_row] = word;
         }
         // Tell the owner's GEMM launch (which may already be running, on this GPU too)
-        // that one more row of this GEMM row tile has landed: a release, cumulative over
-        // the warp's stores ordered by __syncwarp.
-        __syncwarp();
-        if (lane == 0) {
-            uint32_t* const arrived = reinterpret_cast<uint32_t*>(dst_arena + p.off_exchange + exchange::kTileArrived) +
-                                      gen * exchange::kMaxRowTiles + first_tile[e] + pos / tn;
-            if (P > 1) ptx::red_release_sys_add(arrived, 1u);
-            else asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(arrived), "r"(1u) : "memory");
-        }
+        // that one more row of this GEMM row tile has landed: fence + relaxed add, a release
+        // cumulative over the warp's stores ordered by __syncwarp.
+        if (lane == num_pending)
+            pending = reinterpret_cast<uint32_t*>(dst_arena + p.off_exchange + exchange::kTileArrived) +
+                      gen * exchange::kMaxRowTiles + first_tile[e] + pos / tn;
+        if (++num_pending == kArrivalBatch) flush_arrivals();
     }
+    flush_arrivals();
 }
 
 }  // namespace gcmoe

@@ -800,7 +800,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             if (tile >= total_tiles) break;
             const TileCoord tc = locate(tile);
             const GemmSegment& sg = p.seg[tc.seg];
-            const uint32_t b = tc.block, nt = tc.n_tile, e = tc.expert, valid = tc.valid;
+            const uint32_t b = tc.block, nt = tc.n_tile, valid = tc.valid;
             const uint32_t ncols = round_up_u32(valid, 16);
             const uint32_t as = p.acc_stages == 2 ? (it & 1u) : 0u;
             const uint32_t acc_phase = p.acc_stages == 2 ? ((it >> 1) & 1u) : (it & 1u);
