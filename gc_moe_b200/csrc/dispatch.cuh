@@ -365,7 +365,7 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
     }
     __syncthreads();
 
-    // One warp per route: copy the FP8 row (16 bytes per lane per step), scatter
+    // One warp per route: copy the FP8 row (16 bytes per lane and load), scatter
     // its packed scale words into the owner's MN-major scale ring, then tell the
     // owner one more row of that expert has landed.
     const uint32_t row_vecs = p.hidden / 16, sf_words = p.hidden / 128;
@@ -394,15 +394,19 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         const uint32_t t = a / p.topk;
         const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(t) * p.hidden);
         uint4* dst = reinterpret_cast<uint4*>(dst_arena + p.off_l1_acts + static_cast<size_t>(row) * p.hidden);
-        // eight 16-byte loads in flight per lane before the first store: one memory
-        // latency per 4 KiB of row instead of one per 512 bytes
-        for (uint32_t v0 = lane; v0 < row_vecs; v0 += 256) {
-            uint4 part[8];
+        // The row's first 64 scale words and sixteen 16-byte loads per lane are in flight
+        // before the first store: one memory latency per 8 KiB of row.
+        uint32_t sf_first[2];
 #pragma unroll
-            for (uint32_t j = 0; j < 8; ++j)
+        for (uint32_t j = 0; j < 2; ++j)
+            if (lane + j * 32 < sf_words) sf_first[j] = p.x_sf[static_cast<size_t>(t) * sf_words + lane + j * 32];
+        for (uint32_t v0 = lane; v0 < row_vecs; v0 += 512) {
+            uint4 part[16];
+#pragma unroll
+            for (uint32_t j = 0; j < 16; ++j)
                 if (v0 + j * 32 < row_vecs) part[j] = src[v0 + j * 32];
 #pragma unroll
-            for (uint32_t j = 0; j < 8; ++j)
+            for (uint32_t j = 0; j < 16; ++j)
                 if (v0 + j * 32 < row_vecs) dst[v0 + j * 32] = part[j];
         }
         const uint32_t block = row / bm, u = row - block * bm;
@@ -413,8 +417,8 @@ dispatch_kernel(const __grid_constant__ DispatchParams p) {
         const uint32_t pos = slice_pos[a - lo];
         const uint32_t tile_row = p.private_sf_row + first_sf[e] + (pos / tn) * round_up_u32(tn, 128) +
                                   sf_row_in_block(pos % tn);
-        for (uint32_t w = lane; w < sf_words; w += 32) {
-            const uint32_t word = p.x_sf[static_cast<size_t>(t) * sf_words + w];
+        for (uint32_t w = lane, j = 0; w < sf_words; w += 32, ++j) {
+            const uint32_t word = j == 0 ? sf_first[0] : j == 1 ? sf_first[1] : p.x_sf[static_cast<size_t>(t) * sf_words + w];
             sf_dst[static_cast<size_t>(w) * p.sf_ring + sf_row] = word;
             if (tile_ordered) sf_dst[static_cast<size_t>(w) * p.sf_ring + tile_row] = word;
         }
