@@ -97,6 +97,41 @@ def sf_rows_of_pool(rows, bm):
     return np.array([(r // bm) * round_up(bm, 128) + sf_row_in_block(r % bm) for r in rows], dtype=np.int64)
 
 
+def check_requantised_intermediate(prod, ref, bm, name, max_fraction=1e-3):
+    """The FP8 bytes and UE8M0 scale bytes of the requantised gate/up output against the oracle's,
+    every mismatch counted and classified.
+
+    The tensor core adds the products of a K block, and the K blocks of a row, in an order of its
+    own; the oracle sums in numpy's.  The FP32 accumulators therefore differ in their last bits,
+    and an element that sits on a rounding boundary -- of the BF16 rounding in front of SwiGLU or
+    of the FP8 rounding behind it -- may come out one FP8 code away (a BF16 step is 2^-8 of the
+    value, an e4m3 step 2^-3, so two flipped BF16 roundings still cross at most one FP8
+    boundary).  When the element is the largest of its group of 32 and sits on a power of two,
+    the group's scale byte moves by one and the group's payload bytes with it.  Nothing else is
+    accepted: scale bytes differ by at most one; where the scale byte agrees a payload byte
+    differs by at most one code (the sign only between the two zeros and the smallest
+    magnitudes); and both kinds stay below ``max_fraction`` of their population.
+    """
+    valid = np.nonzero(ref.dispatch[0].metadata[:, 0] >= 0)[0]
+    got = prod['l2_acts'][valid]
+    want = ref.l2_acts[0].view(torch.uint8).numpy()[valid]
+    got_sf = prod['l2_acts_sf'][sf_rows_of_pool(valid, bm)].reshape(len(valid), -1)
+    want_sf = ref.l2_sf[0].numpy()[valid]
+    assert got.shape == want.shape and got_sf.shape == want_sf.shape
+    sf_delta = got_sf.astype(np.int16) - want_sf.astype(np.int16)
+    assert np.abs(sf_delta).max(initial=0) <= 1
+    moved = sf_delta != 0
+    same_scale = ~np.repeat(moved, 32, axis=1)
+    differs = (got != want) & same_scale
+    got_mag, want_mag = (got & 0x7F).astype(np.int16), (want & 0x7F).astype(np.int16)
+    sign_differs = ((got ^ want) & 0x80) != 0
+    one_step = (np.abs(got_mag - want_mag) <= 1) & (~sign_differs | (got_mag + want_mag <= 1))
+    assert one_step[differs].all()
+    print(f'PARITY {name}: requantised intermediate: {int(differs.sum())} of {differs.size} payload bytes '
+          f'one code away, {int(moved.sum())} of {moved.size} scale bytes one step away')
+    assert moved.sum() <= max_fraction * moved.size and differs.sum() <= max_fraction * differs.size
+
+
 def check_dispatch_products(prod, d, bm):
     """Exact comparison of the arena's dispatch data products with the oracle's."""
     assert np.array_equal(prod['counts'], d.counts[0])

@@ -13,7 +13,7 @@ import torch
 
 from oracle import gcmoe_oracle as O
 
-from _cases import LayerCase, check_dispatch_products, sf_rows_of_pool
+from _cases import LayerCase, check_dispatch_products, check_requantised_intermediate, sf_rows_of_pool
 
 pytestmark = pytest.mark.gpu
 
@@ -56,10 +56,7 @@ def test_config0_bit_exact_products_and_output(small):
     prod = small.products(16, gen)
     check_dispatch_products(prod, ref.dispatch[0], bm)
     assert np.array_equal(stats.cpu().numpy(), ref.stats[0])
-    valid = np.nonzero(ref.dispatch[0].metadata[:, 0] >= 0)[0]
-    assert (prod['l2_acts'][valid] == ref.l2_acts[0].view(torch.uint8).numpy()[valid]).mean() > 0.999
-    got_sf = prod['l2_acts_sf'][sf_rows_of_pool(valid, bm)].reshape(len(valid), -1)
-    assert (got_sf == ref.l2_sf[0].numpy()[valid]).mean() > 0.999
+    check_requantised_intermediate(prod, ref, bm, 'config 0')
     assert_close(y, ref.y[0])
     # nothing outside y[:T] is written
     guard = small.full_y.cpu()
@@ -72,7 +69,9 @@ def test_config1_token_sweep(config1, tokens):
     gen = parity(config1) & 1
     y = config1.run(xq, xsf, idx, w)
     ref = config1.oracle(xq, xsf, idx, w)
-    check_dispatch_products(config1.products(tokens, gen), ref.dispatch[0], config1.block_m(tokens))
+    prod = config1.products(tokens, gen)
+    check_dispatch_products(prod, ref.dispatch[0], config1.block_m(tokens))
+    check_requantised_intermediate(prod, ref, config1.block_m(tokens), f'config 1 T={tokens}')
     assert_close(y, ref.y[0])
 
 
