@@ -17,7 +17,8 @@
 // Each warp then pushes whole rows -- FP8 payload, packed scale words, route
 // weight, source metadata, index-table entry -- straight to their final place
 // in the owner's arena (16-byte stores over NVLink, local stores on one rank)
-// and bumps the owner's per-expert arrival counter with a system-scope release.
+// and bumps the owner's arrival counter of the GEMM row tile the row belongs to
+// (a system-scope fence and relaxed adds, once per four rows of the warp).
 // The reference instead writes indices, waits for every rank's counts and then
 // PULLS each row with a remote read (impls:997-1094): one more NVLink trip on
 // the critical path.
