@@ -97,7 +97,7 @@ def sf_rows_of_pool(rows, bm):
     return np.array([(r // bm) * round_up(bm, 128) + sf_row_in_block(r % bm) for r in rows], dtype=np.int64)
 
 
-def check_requantised_intermediate(prod, ref, bm, name, max_fraction=1e-3):
+def check_requantised_intermediate(prod, ref, bm, name, max_fraction=1e-5):
     """The FP8 bytes and UE8M0 scale bytes of the requantised gate/up output against the oracle's,
     every mismatch counted and classified.
 
@@ -110,7 +110,10 @@ def check_requantised_intermediate(prod, ref, bm, name, max_fraction=1e-3):
     the group's scale byte moves by one and the group's payload bytes with it.  Nothing else is
     accepted: scale bytes differ by at most one; where the scale byte agrees a payload byte
     differs by at most one code (the sign only between the two zeros and the smallest
-    magnitudes); and both kinds stay below ``max_fraction`` of their population.
+    magnitudes); and each kind stays below ``max_fraction`` of its population (or two, for
+    small populations).  Measured on B200: none at 16 tokens of the small configuration and at
+    1 and 8 tokens of the single-GPU benchmark geometry, 1, 1 and 4 payload bytes of 0.5, 2.1
+    and 4.2 million at 32, 128 and 256 tokens, no scale byte.
     """
     valid = np.nonzero(ref.dispatch[0].metadata[:, 0] >= 0)[0]
     got = prod['l2_acts'][valid]
@@ -129,7 +132,7 @@ def check_requantised_intermediate(prod, ref, bm, name, max_fraction=1e-3):
     assert one_step[differs].all()
     print(f'PARITY {name}: requantised intermediate: {int(differs.sum())} of {differs.size} payload bytes '
           f'one code away, {int(moved.sum())} of {moved.size} scale bytes one step away')
-    assert moved.sum() <= max_fraction * moved.size and differs.sum() <= max_fraction * differs.size
+    assert moved.sum() <= max(2, max_fraction * moved.size) and differs.sum() <= max(2, max_fraction * differs.size)
 
 
 def check_dispatch_products(prod, d, bm):
