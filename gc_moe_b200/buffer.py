@@ -1,7 +1,7 @@
 """The symmetric workspace object of the operator API.
 
-Same constructor arguments, attributes and views as the reference's
-``GCSymmBuffer`` (gc_moe/gc/__init__.py:16-163).  Two deliberate differences:
+Same constructor arguments (``base=`` included), attributes and views as the
+reference's ``GCSymmBuffer`` (gc_moe/gc/__init__.py:16-163).  Two deliberate differences:
 the activation rings hold the whole receive pool (no slot reuse inside a
 call, see ``heuristics.full_pool_ring_tokens``), and device-side failures are
 reported through ``raise_on_device_error`` instead of trapping the GPU.
@@ -46,6 +46,13 @@ class GCSymmBuffer:
     with ``u = t % BM`` and BM from ``get_block_m_for_gc_moe``.  Calls that
     share one workspace must be serialised by the caller, and graphs captured
     on it retired before ``destroy()``.
+
+    ``base`` makes this object a second wrapper over the allocation of a live
+    ``GCSymmBuffer`` of the same group and exactly the same geometry instead of
+    allocating (gc_moe/gc/__init__.py:38,73-93): no rendezvous, no zeroing, the
+    protocol state in the arena (call parity, counters) is shared, launch plans
+    are per wrapper.  Calls through all wrappers of one allocation must be
+    serialised; destroying a wrapper leaves the allocation to its owner.
     """
 
     _views = _VIEW_NAMES
@@ -53,9 +60,11 @@ class GCSymmBuffer:
     def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int,
                  num_topk: int, hidden: int, intermediate_hidden: int,
                  num_shared_experts: int = 0, mma_type: str = 'fp8xfp4',
-                 activation: str = 'swiglu'):
+                 activation: str = 'swiglu', base=None):
         if mma_type != 'fp8xfp4' or activation != 'swiglu':
             raise ValueError('GC MoE requires fp8xfp4/swiglu')
+        if base is not None and not isinstance(base, GCSymmBuffer):
+            raise ValueError('base must be a GCSymmBuffer of this package; foreign workspaces are unsupported')
         self.group = group
         self.rank_idx = dist.get_rank(group=group)
         world = group.size()
@@ -70,22 +79,36 @@ class GCSymmBuffer:
         self.layout = GCBufferLayout(world, num_experts, self.num_max_tokens_per_rank,
                                      num_topk, hidden, intermediate_hidden, ring, sf_ring,
                                      num_shared_experts)
-        if world == 1:
-            self.buffer = torch.empty(self.layout.nbytes, dtype=torch.int8, device='cuda')
-            self.handle = types.SimpleNamespace(buffer_ptrs=[self.buffer.data_ptr()])
+        if base is None:
+            if world == 1:
+                self.buffer = torch.empty(self.layout.nbytes, dtype=torch.int8, device='cuda')
+                self.handle = types.SimpleNamespace(buffer_ptrs=[self.buffer.data_ptr()])
+            else:
+                import torch.distributed._symmetric_memory as symm_mem
+                self.buffer = symm_mem.empty(self.layout.nbytes, dtype=torch.int8, device='cuda')
+                self.handle = symm_mem.rendezvous(self.buffer, group=group)
         else:
-            import torch.distributed._symmetric_memory as symm_mem
-            self.buffer = symm_mem.empty(self.layout.nbytes, dtype=torch.int8, device='cuda')
-            self.handle = symm_mem.rendezvous(self.buffer, group=group)
+            if base.buffer is None or base.handle is None or base.group is not group:
+                raise ValueError('base must be a live allocation in the same group')
+            for name in ('num_experts', 'num_max_tokens_per_rank', 'num_topk', 'hidden',
+                         'intermediate_hidden', 'num_shared_experts', 'mma_type', 'activation'):
+                if getattr(base, name) != getattr(self, name):
+                    raise ValueError(f'incompatible base: {name}')
+            if self.layout != base.layout:
+                raise ValueError('incompatible base: GC workspace layout')
+            if self.layout.nbytes > base.buffer.nbytes:
+                raise ValueError('base allocation too small')
+            self.buffer, self.handle = base.buffer, base.handle
         peers = tuple(int(ptr) for ptr in self.handle.buffer_ptrs)
         if (len(peers) != world or any(ptr <= 0 or ptr % 16 for ptr in peers)
                 or peers[self.rank_idx] != self.buffer.data_ptr()):
             raise RuntimeError('symmetric rendezvous returned invalid peer addresses')
         self.peer_addresses = peers
-        self.buffer.zero_()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier(group=group)
+        if base is None:
+            self.buffer.zero_()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier(group=group)
         _typed_views(self.buffer, self.layout, self)
         self._plans = {}          # launch plans cached per call signature
         self._retired_scratch = []   # scratch blocks of evicted plans, until their status has been read
@@ -161,5 +184,7 @@ def get_symm_buffer_for_gc_moe(group, num_experts: int, num_max_tokens_per_rank:
                                num_topk: int, hidden: int, intermediate_hidden: int,
                                num_shared_experts: int = 0, mma_type: str = 'fp8xfp4',
                                activation: str = 'swiglu') -> GCSymmBuffer:
+    """Allocate a workspace (gc_moe/gc/__init__.py:155-163; like the reference's factory it
+    does not take ``base`` -- construct ``GCSymmBuffer(..., base=owner)`` for a second wrapper)."""
     return GCSymmBuffer(group, num_experts, num_max_tokens_per_rank, num_topk, hidden,
                         intermediate_hidden, num_shared_experts, mma_type, activation)

@@ -64,3 +64,12 @@ def test_timeout_env_parsing(monkeypatch):
         monkeypatch.setenv('GC_MOE_NVLINK_BARRIER_TIMEOUT_SECS', bad)
         with pytest.raises(ValueError):
             _timeout_ms()
+
+
+def test_foreign_base_and_other_recipes_are_rejected_before_anything_is_allocated():
+    """gc_moe/gc/__init__.py:41-44: the recipe check, then the type of ``base``."""
+    from gc_moe_b200 import GCSymmBuffer
+    with pytest.raises(ValueError, match='fp8xfp4/swiglu'):
+        GCSymmBuffer(None, 8, 16, 2, 1024, 512, mma_type='fp8xfp8')
+    with pytest.raises(ValueError, match='foreign workspaces are unsupported'):
+        GCSymmBuffer(None, 8, 16, 2, 1024, 512, base=types.SimpleNamespace(buffer=None))

@@ -371,3 +371,39 @@ def test_expired_wait_is_reported_and_later_calls_return_at_once(single_rank_gro
         assert torch.isnan(y.float()).all()
     finally:
         case.close()
+
+
+def test_second_wrapper_over_the_same_allocation(small, single_rank_group):
+    """``GCSymmBuffer(..., base=owner)`` wraps the owner's bytes without allocating
+    (gc_moe/gc/__init__.py:38,73-93): calls through either wrapper, one after the other,
+    give the oracle's output and keep alternating the call parity they share; a wrapper of
+    another geometry, of a foreign object or of a destroyed owner is rejected."""
+    owner = small.buf
+    args = (single_rank_group, small.e, small.capacity, small.k, small.h, small.i)
+    twin = G.GCSymmBuffer(*args, base=owner)
+    try:
+        assert twin.buffer.data_ptr() == owner.buffer.data_ptr() and twin.peer_addresses == owner.peer_addresses
+        assert twin.layout == owner.layout and twin.x.data_ptr() == owner.x.data_ptr()
+        for step, buf in enumerate((twin, owner, twin, twin, owner)):
+            xq, xsf, idx, w = O.make_tokens(12 + step, small.h, small.e, small.k, seed=900 + step)
+            before = parity(small)
+            small.buf = buf
+            try:
+                y = small.run(xq, xsf, idx, w)
+            finally:
+                small.buf = owner
+            assert parity(small) == before + 1
+            assert_close(y, small.oracle(xq, xsf, idx, w).y[0])
+        with pytest.raises(ValueError, match='incompatible base'):
+            G.GCSymmBuffer(single_rank_group, small.e, small.capacity, small.k, small.h, 2 * small.i, base=owner)
+        with pytest.raises(ValueError, match='base must be'):
+            G.GCSymmBuffer(*args, base=owner.buffer)
+        dead = G.GCSymmBuffer(*args)
+        dead.destroy()
+        with pytest.raises(ValueError, match='live allocation'):
+            G.GCSymmBuffer(*args, base=dead)
+    finally:
+        twin.destroy()
+    assert owner.buffer is not None      # destroying a wrapper leaves the allocation to its owner
+    xq, xsf, idx, w = O.make_tokens(5, small.h, small.e, small.k, seed=950)
+    assert_close(small.run(xq, xsf, idx, w), small.oracle(xq, xsf, idx, w).y[0])
