@@ -11,6 +11,7 @@ import numpy as np
 import pytest
 import torch
 
+import gc_moe_b200 as G
 from oracle import gcmoe_oracle as O
 
 from _cases import LayerCase, check_dispatch_products, check_requantised_intermediate, sf_rows_of_pool
